@@ -41,12 +41,25 @@ class Config:
                                                            # every rank: one exchange per block, any tp in {2,4,8});
                                                            # None: shard when the heads divide, else replicate
 
+    dtype: str = "bfloat16"                                # layered hybrid decoders: "bfloat16" (serving) or "float32" (all fp32)
+    num_state_slots: int = 0                               # recurrent-state slots (0 = one per max_num_seqs, at most 64)
+
     tp_devices: Any = None                                 # CUDA device of every rank when the ranks are threads of this
                                                            # process (default: rank r -> device r mod device count)
 
     def __post_init__(self):
         self.model = _resolve_checkpoint_dir(self.model)
-        if self.kvcache_block_size % 256:
+        from .registry import resolve
+        family = resolve(self.model) if self.hf_config is None else None
+        if self.hf_config is None and family is not None and family.native_config:
+            if self.model is None or not os.path.isdir(self.model):
+                raise AssertionError(f"Model path does not exist: {self.model}")
+            self.hf_config = family.load_config(self.model)
+        native = bool(getattr(self.hf_config, "is_hybrid", False))
+        if native:
+            if self.kvcache_block_size <= 0 or self.kvcache_block_size % 16:
+                raise AssertionError("kvcache_block_size must be a positive multiple of 16")
+        elif self.kvcache_block_size % 256:
             raise AssertionError("kvcache_block_size must be a multiple of 256")
         if not 1 <= self.tensor_parallel_size <= 8:
             raise AssertionError("tensor_parallel_size must lie in [1, 8]")
@@ -56,7 +69,7 @@ class Config:
             from transformers import AutoConfig
             self.hf_config = AutoConfig.from_pretrained(self.model)
         self.max_model_len = min(self.max_model_len, self.hf_config.max_position_embeddings)
-        if self.max_num_batched_tokens < self.max_model_len:
+        if not native and self.max_num_batched_tokens < self.max_model_len:
             raise AssertionError("max_num_batched_tokens must cover max_model_len")
 
 

@@ -1,0 +1,551 @@
+// hy_engine.cu — host side of libjf_hybrid.so (include/jacobi_hybrid.h): weights by checkpoint name, merged projections,
+// the paged key cache, recurrent-state slots and the step function that runs a packed batch of entries through the layers.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/jacobi_hybrid.h"
+#include "hy_kernels.cuh"
+
+namespace hy {
+
+struct HostTensor {
+  std::vector<int64_t> shape;
+  std::vector<float> v;
+  int64_t rows() const { return shape.empty() ? 1 : shape[0]; }
+  int64_t cols() const { return shape.size() < 2 ? 1 : shape[1]; }
+};
+
+// Device tensors of one layer (WT = operand type of the build; fp32 tables where the design wants fp32).
+struct LayerW {
+  void* norm1 = nullptr;
+  void* w_in = nullptr;   int n_in = 0;        // merged projections of the normed input [n_in, width]
+  void* w_out = nullptr;  int k_out = 0;       // merged output projections [width, k_out] (concatenated along k)
+  // column offsets inside the merged input projection / the merged output operand
+  int c_q = 0, c_k = 0, c_g = 0, c_x = 0, c_z = 0, c_v = 0, c_b = 0, c_a1 = 0, c_g1 = 0, c_up = 0;
+  int o_mix = 0, o_scan = 0, o_ff = 0;
+  void* conv_qk = nullptr; void* sink = nullptr;                               // attention side
+  void* conv_x = nullptr; void* conv_xb = nullptr; void* w_x = nullptr; void* w_dt = nullptr; void* dt_b = nullptr;
+  float* A_neg = nullptr; void* D = nullptr;                                    // scan side
+  void* conv_qkv = nullptr; void* w_a2 = nullptr; void* w_g2 = nullptr; void* A_log = nullptr; void* dt_bias = nullptr;
+  void* norm_w = nullptr;                                                        // delta
+  void* cache = nullptr;                                                         // key pages of this layer
+  float* conv_state = nullptr; float* conv_state2 = nullptr; float* rec_state = nullptr;
+};
+
+}  // namespace hy
+
+using namespace hy;
+
+struct hy_engine {
+  hy_model_cfg m{};
+  hy_runtime_cfg rt{};
+  std::vector<hy_layer_cfg> lc;
+  std::map<std::string, HostTensor> host;
+  std::vector<LayerW> lw;
+  void* embed = nullptr; void* final_norm = nullptr; void* head = nullptr; float* inv_freq = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::string err;
+  int64_t launches = 0;
+  float last_ms = 0.0f;
+  int64_t bytes_w = 0, bytes_cache = 0, bytes_state = 0, bytes_ws = 0;
+  std::vector<void*> allocs;
+  bool finalized = false;
+  // workspace
+  float* x = nullptr; void* hbuf = nullptr; void* pin = nullptr; void* cat = nullptr; void* cv = nullptr;
+  float* f1 = nullptr; float* f2 = nullptr; void* hw = nullptr; float* logits = nullptr; int* sampled = nullptr;
+  float* temp_d = nullptr;
+  int ld_pin = 0, ld_cat = 0, ld_cv = 0, ld_f1 = 0, ld_f2 = 0;
+  int* meta_d = nullptr; int* meta_h = nullptr; size_t meta_words = 0;
+  size_t esz() const { return m.dtype == HY_DTYPE_F32 ? 4 : 2; }
+};
+
+#define HY_CUDA(call)                                                                                   \
+  do {                                                                                                  \
+    cudaError_t e_ = (call);                                                                            \
+    if (e_ != cudaSuccess) {                                                                            \
+      h->err = std::string(#call) + ": " + cudaGetErrorString(e_);                                      \
+      return HY_ERR_CUDA;                                                                               \
+    }                                                                                                   \
+  } while (0)
+
+static int fail(hy_engine* h, int code, const std::string& msg) {
+  h->err = msg;
+  return code;
+}
+
+static int dev_alloc(hy_engine* h, void** p, size_t bytes, int64_t* counter) {
+  if (bytes == 0) bytes = 16;
+  HY_CUDA(cudaMalloc(p, bytes));
+  h->allocs.push_back(*p);
+  *counter += (int64_t)bytes;
+  return HY_OK;
+}
+
+static thread_local std::string g_create_err;
+
+extern "C" int hy_create(const hy_model_cfg* model, const hy_layer_cfg* layers, const hy_runtime_cfg* rt, hy_handle* out) {
+  if (!model || !layers || !rt || !out) { g_create_err = "null argument"; return HY_ERR_INVALID; }
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+    g_create_err = "no CUDA device: the hybrid engine has no CPU fallback";
+    return HY_ERR_CUDA;
+  }
+  hy_engine* h = new hy_engine();
+  h->m = *model;
+  h->rt = *rt;
+  h->lc.assign(layers, layers + model->n_layers);
+  auto bad = [&](const std::string& s) { g_create_err = s; delete h; return HY_ERR_INVALID; };
+  if (model->dtype != HY_DTYPE_BF16 && model->dtype != HY_DTYPE_F32) return bad("dtype must be bf16 or f32");
+  if (rt->page_size <= 0 || rt->page_size % 16) return bad("page_size must be a positive multiple of 16");
+  for (auto& c : h->lc) {
+    if (c.mixer == HY_MIX_ATTN_SCAN) {
+      if (c.a_vdim != c.a_dim) return bad("attention whose values are its keys needs vdim == dim");
+      if (c.a_dim > 32 * HY_ATT_MAXD) return bad("attention key size above 256");
+      if (c.a_kv_heads <= 0 || c.a_heads % c.a_kv_heads) return bad("attention heads must be a multiple of kv_heads");
+      if (c.s_state > 256 || c.s_state <= 0) return bad("scan state size must lie in 1..256");
+      if (c.a_conv > HY_MAX_TAPS || c.s_conv > HY_MAX_TAPS || c.a_conv < 1 || c.s_conv < 1) return bad("conv taps must lie in 1..16");
+    } else if (c.mixer == HY_MIX_DELTA) {
+      if (c.d_kv_heads <= 0 || c.d_heads % c.d_kv_heads) return bad("delta heads must be a multiple of kv_heads");
+      if (c.d_dim > 1024 || c.d_vdim > 1024) return bad("delta head sizes above 1024");
+      if ((size_t)c.d_dim * c.d_vdim * 4 > 200 * 1024) return bad("delta state of one head exceeds shared memory");
+      if (c.d_conv > HY_MAX_TAPS || c.d_conv < 1) return bad("conv taps must lie in 1..16");
+    } else {
+      return bad("unknown mixer kind");
+    }
+  }
+  if (cudaSetDevice(rt->device) != cudaSuccess) return bad("cudaSetDevice failed");
+  cudaStreamCreate(&h->stream);
+  cudaEventCreate(&h->ev0);
+  cudaEventCreate(&h->ev1);
+  *out = h;
+  return HY_OK;
+}
+
+extern "C" void hy_destroy(hy_handle h) {
+  if (!h) return;
+  cudaSetDevice(h->rt.device);
+  cudaStreamSynchronize(h->stream);
+  for (void* p : h->allocs) cudaFree(p);
+  if (h->meta_h) cudaFreeHost(h->meta_h);
+  cudaEventDestroy(h->ev0);
+  cudaEventDestroy(h->ev1);
+  cudaStreamDestroy(h->stream);
+  delete h;
+}
+
+extern "C" const char* hy_last_error(hy_handle h) { return h ? h->err.c_str() : g_create_err.c_str(); }
+extern "C" int64_t hy_launch_count(hy_handle h) { return h ? h->launches : 0; }
+extern "C" float hy_last_step_ms(hy_handle h) { return h ? h->last_ms : 0.0f; }
+extern "C" int hy_memory_info(hy_handle h, int64_t* w, int64_t* c, int64_t* s, int64_t* ws) {
+  if (!h) return HY_ERR_INVALID;
+  if (w) *w = h->bytes_w;
+  if (c) *c = h->bytes_cache;
+  if (s) *s = h->bytes_state;
+  if (ws) *ws = h->bytes_ws;
+  return HY_OK;
+}
+
+extern "C" int hy_load_tensor(hy_handle h, const char* name, const void* data, const int64_t* shape, int32_t ndim, int32_t dtype) {
+  if (!h || !name || !data) return HY_ERR_INVALID;
+  if (h->finalized) return fail(h, HY_ERR_INVALID, "weights are final");
+  HostTensor t;
+  int64_t n = 1;
+  for (int i = 0; i < ndim; ++i) { t.shape.push_back(shape[i]); n *= shape[i]; }
+  t.v.resize((size_t)n);
+  if (dtype == HY_DTYPE_F32) {
+    memcpy(t.v.data(), data, (size_t)n * 4);
+  } else if (dtype == HY_DTYPE_BF16) {
+    const uint16_t* s = (const uint16_t*)data;
+    for (int64_t i = 0; i < n; ++i) { uint32_t u = (uint32_t)s[i] << 16; memcpy(&t.v[(size_t)i], &u, 4); }
+  } else if (dtype == HY_DTYPE_F16) {
+    const __half* s = (const __half*)data;
+    for (int64_t i = 0; i < n; ++i) t.v[(size_t)i] = __half2float(s[i]);
+  } else if (dtype == HY_DTYPE_I32) {
+    const int32_t* s = (const int32_t*)data;
+    for (int64_t i = 0; i < n; ++i) t.v[(size_t)i] = (float)s[i];
+  } else {
+    return fail(h, HY_ERR_INVALID, "unknown tensor dtype");
+  }
+  h->host[name] = std::move(t);
+  return HY_OK;
+}
+
+// ---- weights -------------------------------------------------------------------------------------------------------------------
+namespace {
+
+struct Builder {
+  hy_engine* h;
+  int rc = HY_OK;
+  const HostTensor* get(const std::string& name, int64_t r, int64_t c) {
+    auto it = h->host.find(name);
+    if (it == h->host.end()) { if (rc == HY_OK) rc = fail(h, HY_ERR_INVALID, "missing tensor " + name); return nullptr; }
+    const HostTensor& t = it->second;
+    if (t.rows() != r || (c >= 0 && t.cols() != c) || (c < 0 && t.shape.size() != 1)) {
+      if (rc == HY_OK) rc = fail(h, HY_ERR_INVALID, "tensor " + name + " has an unexpected shape");
+      return nullptr;
+    }
+    return &t;
+  }
+  // upload as the build's operand type
+  void* up(const std::vector<float>& v) {
+    void* d = nullptr;
+    if (rc != HY_OK) return nullptr;
+    if (h->m.dtype == HY_DTYPE_F32) {
+      if (dev_alloc(h, &d, v.size() * 4, &h->bytes_w) != HY_OK) { rc = HY_ERR_CUDA; return nullptr; }
+      cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice);
+    } else {
+      std::vector<__nv_bfloat16> b(v.size());
+      for (size_t i = 0; i < v.size(); ++i) b[i] = __float2bfloat16_rn(v[i]);
+      if (dev_alloc(h, &d, v.size() * 2, &h->bytes_w) != HY_OK) { rc = HY_ERR_CUDA; return nullptr; }
+      cudaMemcpy(d, b.data(), b.size() * 2, cudaMemcpyHostToDevice);
+    }
+    return d;
+  }
+  float* up_f32(const std::vector<float>& v) {
+    void* d = nullptr;
+    if (rc != HY_OK) return nullptr;
+    if (dev_alloc(h, &d, v.size() * 4, &h->bytes_w) != HY_OK) { rc = HY_ERR_CUDA; return nullptr; }
+    cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice);
+    return (float*)d;
+  }
+};
+
+// rows of several [n_i, k] matrices stacked
+void stack_rows(std::vector<float>& dst, const HostTensor* t) { if (t) dst.insert(dst.end(), t->v.begin(), t->v.end()); }
+
+}  // namespace
+
+extern "C" int hy_finalize(hy_handle h) {
+  if (!h) return HY_ERR_INVALID;
+  if (h->finalized) return HY_OK;
+  HY_CUDA(cudaSetDevice(h->rt.device));
+  Builder B{h};
+  const int W = h->m.width, V = h->m.vocab;
+  const hy_runtime_cfg& rt = h->rt;
+  if (auto t = B.get("embed", V, W)) h->embed = B.up(t->v);
+  if (auto t = B.get("final.norm", W, -1)) h->final_norm = B.up(t->v);
+  if (auto t = B.get("head", V, W)) h->head = B.up(t->v);
+  {
+    std::vector<float> f((W + 1) / 2);
+    for (size_t i = 0; i < f.size(); ++i) f[i] = (float)pow(10000.0, -2.0 * (double)i / (double)W);
+    h->inv_freq = B.up_f32(f);
+  }
+  h->lw.resize(h->lc.size());
+  int max_in = 1, max_out = 1, max_cv = 1, max_f1 = 1, max_f2 = 1;
+  for (size_t i = 0; i < h->lc.size() && B.rc == HY_OK; ++i) {
+    const hy_layer_cfg& c = h->lc[i];
+    LayerW& L = h->lw[i];
+    const std::string p = "l" + std::to_string(i) + ".";
+    if (auto t = B.get(p + "norm1", W, -1)) L.norm1 = B.up(t->v);
+    const int ff = c.ff_kind == HY_FF_NONE ? 0 : c.ff;
+    std::vector<float> win, wout;
+    int n_in = 0;
+    std::vector<const HostTensor*> outs;       // output projections to concatenate along k
+    if (c.mixer == HY_MIX_ATTN_SCAN) {
+      const std::string a = p + "mix.left.", s = p + "mix.right.";
+      const int nq = c.a_heads * c.a_dim, nk = c.a_kv_heads * c.a_dim, nv = c.a_heads * c.a_vdim;
+      const int R = c.s_dt_rank, N = c.s_state, I = c.s_inner;
+      L.c_q = n_in; stack_rows(win, B.get(a + "q", nq, W)); n_in += nq;
+      L.c_k = n_in; stack_rows(win, B.get(a + "k", nk, W)); n_in += nk;
+      L.c_g = n_in; stack_rows(win, B.get(a + "g", nv, W)); n_in += nv;
+      L.c_x = n_in; L.c_z = n_in + I; stack_rows(win, B.get(s + "in", 2 * I, W)); n_in += 2 * I;
+      std::vector<float> cw;
+      stack_rows(cw, B.get(a + "q.conv", nq, c.a_conv));
+      stack_rows(cw, B.get(a + "k.conv", nk, c.a_conv));
+      L.conv_qk = B.up(cw);
+      if (auto t = B.get(a + "sink", c.a_heads, -1)) L.sink = B.up(t->v);
+      if (auto t = B.get(s + "conv", I, c.s_conv)) L.conv_x = B.up(t->v);
+      if (auto t = B.get(s + "conv.b", I, -1)) L.conv_xb = B.up(t->v);
+      if (auto t = B.get(s + "x", R + 2 * N, I)) L.w_x = B.up(t->v);
+      if (auto t = B.get(s + "dt", I, R)) L.w_dt = B.up(t->v);
+      if (auto t = B.get(s + "dt.b", I, -1)) L.dt_b = B.up(t->v);
+      if (auto t = B.get(s + "A_log", I, N)) {
+        std::vector<float> an(t->v.size());
+        for (size_t j = 0; j < an.size(); ++j) an[j] = -expf(t->v[j]);
+        L.A_neg = B.up_f32(an);
+      }
+      if (auto t = B.get(s + "D", I, -1)) L.D = B.up(t->v);
+      outs.push_back(B.get(a + "o", W, nv));
+      outs.push_back(B.get(s + "o", W, I));
+      L.o_mix = 0; L.o_scan = nv; L.o_ff = nv + I;
+      max_cv = std::max(max_cv, std::max(nq + nk, I));
+      max_f1 = std::max(max_f1, R + 2 * N);
+      max_f2 = std::max(max_f2, I);
+      // state: conv tails and the scan state, key pages
+      if (dev_alloc(h, (void**)&L.conv_state, (size_t)rt.num_slots * (c.a_conv - 1) * (nq + nk) * 4, &h->bytes_state)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&L.conv_state2, (size_t)rt.num_slots * (c.s_conv - 1) * I * 4, &h->bytes_state)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&L.rec_state, (size_t)rt.num_slots * I * N * 4, &h->bytes_state)) return HY_ERR_CUDA;
+      if (dev_alloc(h, &L.cache, (size_t)rt.num_pages * c.a_kv_heads * rt.page_size * c.a_dim * h->esz(), &h->bytes_cache)) return HY_ERR_CUDA;
+    } else {
+      const std::string d = p + "mix.";
+      const int nq = c.d_kv_heads * c.d_dim, nv = c.d_heads * c.d_vdim;
+      L.c_q = n_in; stack_rows(win, B.get(d + "q", nq, W)); n_in += nq;
+      L.c_k = n_in; stack_rows(win, B.get(d + "k", nq, W)); n_in += nq;
+      L.c_v = n_in; stack_rows(win, B.get(d + "v", nv, W)); n_in += nv;
+      L.c_b = n_in; stack_rows(win, B.get(d + "b", c.d_heads, W)); n_in += c.d_heads;
+      L.c_a1 = n_in; stack_rows(win, B.get(d + "a1", c.d_low_a, W)); n_in += c.d_low_a;
+      L.c_g1 = n_in; stack_rows(win, B.get(d + "g1", c.d_low_g, W)); n_in += c.d_low_g;
+      std::vector<float> cw;
+      stack_rows(cw, B.get(d + "q.conv", nq, c.d_conv));
+      stack_rows(cw, B.get(d + "k.conv", nq, c.d_conv));
+      stack_rows(cw, B.get(d + "v.conv", nv, c.d_conv));
+      L.conv_qkv = B.up(cw);
+      if (auto t = B.get(d + "a2", c.d_heads * c.d_dim, c.d_low_a)) L.w_a2 = B.up(t->v);
+      if (auto t = B.get(d + "g2", nv, c.d_low_g)) L.w_g2 = B.up(t->v);
+      if (auto t = B.get(d + "A_log", c.d_heads, -1)) L.A_log = B.up_f32(t->v);
+      if (auto t = B.get(d + "dt_bias", c.d_heads * c.d_dim, -1)) L.dt_bias = B.up_f32(t->v);
+      if (auto t = B.get(d + "norm", c.d_vdim, -1)) L.norm_w = B.up_f32(t->v);
+      outs.push_back(B.get(d + "o", W, nv));
+      L.o_mix = 0; L.o_scan = nv; L.o_ff = nv;
+      max_cv = std::max(max_cv, 2 * nq + nv);
+      max_f1 = std::max(max_f1, c.d_heads * c.d_dim);
+      max_f2 = std::max(max_f2, nv);
+      if (dev_alloc(h, (void**)&L.conv_state, (size_t)rt.num_slots * (c.d_conv - 1) * (2 * nq + nv) * 4, &h->bytes_state)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&L.rec_state, (size_t)rt.num_slots * c.d_heads * c.d_dim * c.d_vdim * 4, &h->bytes_state)) return HY_ERR_CUDA;
+    }
+    L.c_up = n_in;
+    if (ff) {
+      stack_rows(win, B.get(p + "mlp.up", ff, W));
+      outs.push_back(B.get(p + "mlp.down", W, ff));
+      n_in += ff;
+    }
+    if (B.rc != HY_OK) break;
+    L.n_in = n_in;
+    L.w_in = B.up(win);
+    int k_out = 0;
+    for (auto t : outs) k_out += (int)t->cols();
+    L.k_out = k_out;
+    wout.resize((size_t)W * k_out);
+    int off = 0;
+    for (auto t : outs) {
+      const int kc = (int)t->cols();
+      for (int r = 0; r < W; ++r) memcpy(&wout[(size_t)r * k_out + off], &t->v[(size_t)r * kc], (size_t)kc * 4);
+      off += kc;
+    }
+    L.w_out = B.up(wout);
+    max_in = std::max(max_in, L.c_up);
+    max_out = std::max(max_out, k_out);
+  }
+  if (B.rc != HY_OK) return B.rc;
+  h->host.clear();
+  // workspace
+  const size_t T = (size_t)rt.max_step_tokens, es = h->esz();
+  auto r8 = [](int v) { return (v + 7) & ~7; };
+  h->ld_pin = r8(max_in); h->ld_cat = r8(max_out); h->ld_cv = r8(max_cv); h->ld_f1 = r8(max_f1); h->ld_f2 = r8(max_f2);
+  if (dev_alloc(h, (void**)&h->x, T * W * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (dev_alloc(h, &h->hbuf, T * W * es, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (dev_alloc(h, &h->pin, T * h->ld_pin * es, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (dev_alloc(h, &h->cat, T * h->ld_cat * es, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (dev_alloc(h, &h->cv, T * h->ld_cv * es, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (dev_alloc(h, (void**)&h->f1, T * h->ld_f1 * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (dev_alloc(h, (void**)&h->f2, T * h->ld_f2 * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+  const size_t mw = (size_t)rt.max_want;
+  if (dev_alloc(h, &h->hw, mw * W * es, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (dev_alloc(h, (void**)&h->logits, mw * V * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (dev_alloc(h, (void**)&h->sampled, mw * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (dev_alloc(h, (void**)&h->temp_d, mw * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+  h->meta_words = 3 * T + 3 * (size_t)rt.max_step_entries + 1 + (size_t)rt.max_step_entries * rt.max_pages_per_seq + mw;
+  if (dev_alloc(h, (void**)&h->meta_d, h->meta_words * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+  HY_CUDA(cudaMallocHost((void**)&h->meta_h, h->meta_words * 4));
+  HY_CUDA(cudaDeviceSynchronize());
+  h->finalized = true;
+  return HY_OK;
+}
+
+// ---- launches ---------------------------------------------------------------------------------------------------------------------
+namespace {
+
+template <typename TA, typename TW, typename TO>
+int gemm(hy_engine* h, const TA* A, int lda, const TW* Wt, int ldw, int T, int N, int K, GemmOut o) {
+  if (T <= 0 || N <= 0) return HY_OK;
+  if (o.alpha == 0.0f) o.alpha = 1.0f;
+  if (T <= 8 && (size_t)8 * K * 4 <= 160 * 1024) {
+    const int nw = 8;
+    const int blocks = std::min((N + nw - 1) / nw, 148 * 8);
+    auto launch = [&](auto kern, int rows) {
+      const size_t smem = (size_t)rows * K * 4;
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      kern<<<dim3(blocks, (T + rows - 1) / rows), 256, smem, h->stream>>>(A, lda, Wt, ldw, T, N, K, o);
+    };
+    if (T == 1) launch(gemm_rows_kernel<TA, TW, TO, 1>, 1);
+    else if (T == 2) launch(gemm_rows_kernel<TA, TW, TO, 2>, 2);
+    else if (T <= 4) launch(gemm_rows_kernel<TA, TW, TO, 4>, 4);
+    else launch(gemm_rows_kernel<TA, TW, TO, 8>, 8);
+  } else {
+    gemm_simt_kernel<TA, TW, TO><<<dim3((N + 63) / 64, (T + 63) / 64), 256, 0, h->stream>>>(A, lda, Wt, ldw, T, N, K, o);
+  }
+  h->launches++;
+  return HY_OK;
+}
+
+GemmOut to_buf(void* out, int ld) { return GemmOut{out, ld, 1 << 30, nullptr, 0, 0, nullptr, 0, 1.0f}; }
+
+template <typename AT>
+int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float* layers_out) {
+  typedef AT WT;
+  const int W = h->m.width, T = b.T, E = b.E;
+  const float eps = h->m.norm_eps;
+  cudaStream_t s = h->stream;
+  AT* hb = (AT*)h->hbuf; AT* pin = (AT*)h->pin; AT* cat = (AT*)h->cat; AT* cv = (AT*)h->cv;
+  embed_kernel<WT><<<T, 128, 0, s>>>(b, (const WT*)h->embed, h->inv_freq, h->m.emb_scale, W, h->x);
+  h->launches++;
+  for (size_t li = 0; li < h->lc.size(); ++li) {
+    const hy_layer_cfg& c = h->lc[li];
+    const LayerW& L = h->lw[li];
+    const int ff = c.ff_kind == HY_FF_NONE ? 0 : c.ff;
+    rmsnorm_kernel<WT, AT><<<T, 256, 0, s>>>(h->x, nullptr, (const WT*)L.norm1, eps, W, hb);
+    h->launches++;
+    // every projection that reads the normed input, in one product; the feed-forward's hidden part leaves activated,
+    // straight into the operand of the merged output projection
+    GemmOut o_in{pin, h->ld_pin, L.c_up, cat + L.o_ff, h->ld_cat, 1, nullptr, 0, 1.0f};
+    gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, o_in);
+    if (c.mixer == HY_MIX_ATTN_SCAN) {
+      const int nq = c.a_heads * c.a_dim, nk = c.a_kv_heads * c.a_dim, I = c.s_inner, N = c.s_state, R = c.s_dt_rank;
+      // attention side: conv over q | k, keys into their pages, attention over the pages
+      conv_kernel<AT, WT><<<dim3((nq + nk + 127) / 128, T), 128, 0, s>>>(b, pin, h->ld_pin, L.c_q, nq + nk, c.a_conv,
+          (const WT*)L.conv_qk, (const WT*)nullptr, 0, L.conv_state, cv, h->ld_cv);
+      conv_tail_kernel<AT><<<dim3((nq + nk + 127) / 128, E), 128, 0, s>>>(b, pin, h->ld_pin, L.c_q, nq + nk, c.a_conv, L.conv_state);
+      cache_append_kernel<AT><<<T, 128, 0, s>>>(b, cv, h->ld_cv, nq, c.a_kv_heads, c.a_dim, (AT*)L.cache);
+      attn_sink_kernel<AT, WT><<<(T * c.a_heads + 3) / 4, 128, 4 * c.a_dim * sizeof(float), s>>>(
+          b, cv, h->ld_cv, (const AT*)L.cache, (const WT*)L.sink, pin + L.c_g, h->ld_pin, c.a_heads, c.a_kv_heads, c.a_dim,
+          c.a_scale, c.a_qt_coef, c.a_qt_every, c.left_scale, cat + L.o_mix, h->ld_cat);
+      h->launches += 4;
+      // scan side
+      conv_kernel<AT, WT><<<dim3((I + 127) / 128, T), 128, 0, s>>>(b, pin, h->ld_pin, L.c_x, I, c.s_conv, (const WT*)L.conv_x,
+                                                                   (const WT*)L.conv_xb, 1, L.conv_state2, cv, h->ld_cv);
+      conv_tail_kernel<AT><<<dim3((I + 127) / 128, E), 128, 0, s>>>(b, pin, h->ld_pin, L.c_x, I, c.s_conv, L.conv_state2);
+      h->launches += 2;
+      gemm<AT, WT, float>(h, cv, h->ld_cv, (const WT*)L.w_x, I, T, R + 2 * N, I, to_buf(h->f1, h->ld_f1));
+      gemm<float, WT, float>(h, h->f1, h->ld_f1, (const WT*)L.w_dt, R, T, I, R, to_buf(h->f2, h->ld_f2));
+      {
+        int nper = N <= 128 ? 4 : 8;
+        int lanes = 1;
+        while (lanes * nper < N) lanes <<= 1;
+        dim3 grid((I + 128 / lanes - 1) / (128 / lanes), E);
+        if (nper == 4)
+          scan_kernel<AT, WT, 4><<<grid, 128, 0, s>>>(b, cv, h->ld_cv, pin + L.c_z, h->ld_pin, h->f2, h->ld_f2, (const WT*)L.dt_b,
+              h->f1, h->ld_f1, R, R + N, L.A_neg, (const WT*)L.D, I, N, lanes, c.right_scale, L.rec_state, cat + L.o_scan, h->ld_cat);
+        else
+          scan_kernel<AT, WT, 8><<<grid, 128, 0, s>>>(b, cv, h->ld_cv, pin + L.c_z, h->ld_pin, h->f2, h->ld_f2, (const WT*)L.dt_b,
+              h->f1, h->ld_f1, R, R + N, L.A_neg, (const WT*)L.D, I, N, lanes, c.right_scale, L.rec_state, cat + L.o_scan, h->ld_cat);
+        h->launches++;
+      }
+    } else {
+      const int nq = c.d_kv_heads * c.d_dim, nv = c.d_heads * c.d_vdim, C = 2 * nq + nv;
+      conv_kernel<AT, WT><<<dim3((C + 127) / 128, T), 128, 0, s>>>(b, pin, h->ld_pin, L.c_q, C, c.d_conv, (const WT*)L.conv_qkv,
+                                                                   (const WT*)nullptr, 1, L.conv_state, cv, h->ld_cv);
+      conv_tail_kernel<AT><<<dim3((C + 127) / 128, E), 128, 0, s>>>(b, pin, h->ld_pin, L.c_q, C, c.d_conv, L.conv_state);
+      h->launches += 2;
+      gemm<AT, WT, float>(h, pin + L.c_a1, h->ld_pin, (const WT*)L.w_a2, c.d_low_a, T, c.d_heads * c.d_dim, c.d_low_a,
+                          to_buf(h->f1, h->ld_f1));
+      gemm<AT, WT, float>(h, pin + L.c_g1, h->ld_pin, (const WT*)L.w_g2, c.d_low_g, T, nv, c.d_low_g, to_buf(h->f2, h->ld_f2));
+      const int threads = ((std::max(c.d_dim, c.d_vdim) + 31) / 32) * 32;
+      const size_t smem = ((size_t)c.d_dim * c.d_vdim + 3 * c.d_dim + 40) * 4;
+      cudaFuncSetAttribute(delta_kernel<AT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+      delta_kernel<AT, float><<<dim3(c.d_heads, E), threads, smem, s>>>(
+          b, cv, h->ld_cv, 0, nq, 2 * nq, pin, h->ld_pin, L.c_b, h->f1, h->ld_f1, h->f2, h->ld_f2, (const float*)L.A_log,
+          (const float*)L.dt_bias, (const float*)L.norm_w, c.d_heads, c.d_kv_heads, c.d_dim, c.d_vdim, eps, L.rec_state,
+          cat + L.o_mix, h->ld_cat);
+      h->launches++;
+    }
+    (void)ff;
+    // merged output projections, added to the residual stream
+    GemmOut o_out{nullptr, 0, 0, nullptr, 0, 0, h->x, W, 1.0f};
+    gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_out, L.k_out, T, W, L.k_out, o_out);
+    if (layers_out) {
+      cudaMemcpyAsync(layers_out + li * (size_t)T * W, h->x, (size_t)T * W * 4, cudaMemcpyDeviceToHost, s);
+    }
+  }
+  if (n_want > 0) {
+    rmsnorm_kernel<WT, AT><<<n_want, 256, 0, s>>>(h->x, want_d, (const WT*)h->final_norm, eps, W, (AT*)h->hw);
+    h->launches++;
+    GemmOut o = to_buf(h->logits, h->m.vocab);
+    o.alpha = h->m.logit_scale;
+    gemm<AT, WT, float>(h, (const AT*)h->hw, W, (const WT*)h->head, W, n_want, h->m.vocab, W, o);
+  }
+  return HY_OK;
+}
+
+}  // namespace
+
+extern "C" int hy_step(hy_handle h, int32_t n_entries, const int32_t* tokens, const int32_t* ent_start, const int32_t* ent_pos0,
+                       const int32_t* ent_slot, const int32_t* pages, int32_t n_want, const int32_t* want, float* logits_out,
+                       int32_t* sampled_out, const float* temperature, uint64_t seed, float* layers_out) {
+  if (!h || !h->finalized) return h ? fail(h, HY_ERR_INVALID, "hy_finalize has not run") : HY_ERR_INVALID;
+  if (n_entries <= 0 || !tokens || !ent_start || !ent_pos0 || !ent_slot || !pages) return fail(h, HY_ERR_INVALID, "null argument");
+  const hy_runtime_cfg& rt = h->rt;
+  const int E = n_entries, T = ent_start[E];
+  if (E > rt.max_step_entries) return fail(h, HY_ERR_CAPACITY, "more entries than max_step_entries");
+  if (T <= 0 || T > rt.max_step_tokens) return fail(h, HY_ERR_CAPACITY, "step tokens outside 1..max_step_tokens");
+  if (n_want < 0 || n_want > rt.max_want) return fail(h, HY_ERR_CAPACITY, "more wanted rows than max_want");
+  HY_CUDA(cudaSetDevice(rt.device));
+  // host-side checks of everything a kernel will index with
+  for (int e = 0; e < E; ++e) {
+    const int cnt = ent_start[e + 1] - ent_start[e];
+    if (cnt <= 0 || ent_pos0[e] < 0) return fail(h, HY_ERR_INVALID, "empty entry or negative position");
+    if (ent_slot[e] < 0 || ent_slot[e] >= rt.num_slots) return fail(h, HY_ERR_INVALID, "state slot out of range");
+    for (int f = 0; f < e; ++f)
+      if (ent_slot[f] == ent_slot[e]) return fail(h, HY_ERR_INVALID, "two entries of a step share a state slot");
+    const int need = (ent_pos0[e] + cnt + rt.page_size - 1) / rt.page_size;
+    if (need > rt.max_pages_per_seq) return fail(h, HY_ERR_CAPACITY, "request longer than max_pages_per_seq pages");
+    for (int i = 0; i < need; ++i) {
+      const int pg = pages[(size_t)e * rt.max_pages_per_seq + i];
+      if (pg < 0 || pg >= rt.num_pages) return fail(h, HY_ERR_INVALID, "page id out of range");
+    }
+  }
+  for (int i = 0; i < T; ++i)
+    if (tokens[i] < 0 || tokens[i] >= h->m.vocab) return fail(h, HY_ERR_INVALID, "token id outside the vocabulary");
+  for (int i = 0; i < n_want; ++i)
+    if (want[i] < 0 || want[i] >= T) return fail(h, HY_ERR_INVALID, "wanted row outside the step");
+  // one staging block, one copy
+  int* m = h->meta_h;
+  int* tok = m; int* tok_ent = tok + T; int* tok_pos = tok_ent + T;
+  int* es = tok_pos + T; int* ep = es + E + 1; int* esl = ep + E; int* pg = esl + E;
+  int* wn = pg + (size_t)E * rt.max_pages_per_seq;
+  memcpy(tok, tokens, (size_t)T * 4);
+  for (int e = 0; e < E; ++e) {
+    for (int t = ent_start[e]; t < ent_start[e + 1]; ++t) { tok_ent[t] = e; tok_pos[t] = ent_pos0[e] + t - ent_start[e]; }
+    es[e] = ent_start[e]; ep[e] = ent_pos0[e]; esl[e] = ent_slot[e];
+  }
+  es[E] = T;
+  memcpy(pg, pages, (size_t)E * rt.max_pages_per_seq * 4);
+  if (n_want) memcpy(wn, want, (size_t)n_want * 4);
+  const size_t words = (size_t)(wn - m) + n_want;
+  HY_CUDA(cudaMemcpyAsync(h->meta_d, m, words * 4, cudaMemcpyHostToDevice, h->stream));
+  const int* d = h->meta_d;
+  Batch b;
+  b.tok = d; b.tok_ent = d + T; b.tok_pos = d + 2 * T; b.ent_start = d + 3 * T; b.ent_pos0 = b.ent_start + E + 1;
+  b.ent_slot = b.ent_pos0 + E; b.pages = b.ent_slot + E;
+  b.T = T; b.E = E; b.max_pages = rt.max_pages_per_seq; b.page_size = rt.page_size;
+  const int* want_d = b.pages + (size_t)E * rt.max_pages_per_seq;
+  HY_CUDA(cudaEventRecord(h->ev0, h->stream));
+  if (h->m.dtype == HY_DTYPE_F32) run_step<float>(h, b, n_want, want_d, layers_out);
+  else run_step<__nv_bfloat16>(h, b, n_want, want_d, layers_out);
+  if (n_want > 0 && sampled_out) {
+    const float* td = nullptr;
+    if (temperature) {
+      HY_CUDA(cudaMemcpyAsync(h->temp_d, temperature, (size_t)n_want * 4, cudaMemcpyHostToDevice, h->stream));
+      td = h->temp_d;
+    }
+    sample_kernel<<<n_want, 256, 0, h->stream>>>(h->logits, h->m.vocab, td, seed, h->sampled);
+    h->launches++;
+    HY_CUDA(cudaMemcpyAsync(sampled_out, h->sampled, (size_t)n_want * 4, cudaMemcpyDeviceToHost, h->stream));
+  }
+  HY_CUDA(cudaEventRecord(h->ev1, h->stream));
+  if (n_want > 0 && logits_out)
+    HY_CUDA(cudaMemcpyAsync(logits_out, h->logits, (size_t)n_want * h->m.vocab * 4, cudaMemcpyDeviceToHost, h->stream));
+  HY_CUDA(cudaStreamSynchronize(h->stream));
+  HY_CUDA(cudaGetLastError());
+  cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1);
+  return HY_OK;
+}

@@ -92,16 +92,19 @@ class BlockManager:
         self.used_block_ids.add(block_id)
         return block_id
 
+    def blocks_for(self, n_tokens: int) -> int:
+        return -(-n_tokens // self.block_size)
+
     def can_allocate(self, seq: Sequence) -> bool:
-        return len(self.free_block_ids) >= seq.num_blocks + 1
+        return len(self.free_block_ids) >= self.blocks_for(len(seq)) + 1
 
     def allocate(self, seq: Sequence) -> None:
         """Pages for the whole sequence; leading full pages found in the prefix cache are shared (:135-168)."""
         assert not seq.block_table
         h = -1
         miss = not self.enable_prefix_cache
-        for i in range(seq.num_blocks):
-            token_ids = seq.block(i)
+        for i in range(self.blocks_for(len(seq))):
+            token_ids = seq.token_ids[i * self.block_size:(i + 1) * self.block_size]
             full = len(token_ids) == self.block_size
             h = self.compute_hash(token_ids, h) if (full and self.enable_prefix_cache) else -1
             block_id = self._lookup(h, token_ids) if (h != -1 and not miss) else -1

@@ -8,7 +8,7 @@ from time import perf_counter
 
 from ..config import Config
 from ..sampling_params import SamplingParams
-from .model_runner import ModelRunner
+from ..registry import family_of_config
 from .scheduler import Scheduler
 from .sequence import Sequence
 
@@ -19,7 +19,9 @@ class LLMEngine:
         config = Config(model, **{k: v for k, v in kwargs.items() if k in config_fields})
         self.config = config
         self._exited = False
-        self.model_runner = ModelRunner(config, 0, [])
+        # the model registry picks the per-rank runner (and with it the native library) by the model's description
+        self.family = family_of_config(config.hf_config)
+        self.model_runner = self.family.runner()(config, 0, [])
         self.tokenizer = None
         from ..config import _resolve_checkpoint_dir
         # a training output directory is resolved to its latest checkpoint-N, like config.model
@@ -54,6 +56,14 @@ class LLMEngine:
         self.scheduler.add(Sequence(prompt, sampling_params))
 
     def step(self):
+        if self.family.name == "hybrid":
+            # portions: decoded tokens and slices of prompts in one batch (chunked prefill beside decoding)
+            portions = self.scheduler.schedule_portions()
+            toks = self.model_runner.call("run_portions", portions)
+            self.scheduler.postprocess_portions(portions, toks)
+            outputs = [(seq.seq_id, seq.completion_token_ids) for seq, _ in portions if seq.is_finished]
+            fed = sum(n for (_, n), t in zip(portions, toks) if t is None or n > 1)
+            return outputs, (fed if fed else -sum(t is not None for t in toks))
         seqs, is_prefill = self.scheduler.schedule()
         result = self.model_runner.call("run", seqs, is_prefill)
         if result is None or (is_prefill and len(result) > 0 and result[0] == []):

@@ -13,6 +13,7 @@ from typing import Deque, List, Sequence as Seq, Tuple
 from ..config import Config
 from .block_manager import BlockManager
 from .sequence import Sequence, SequenceStatus
+from .state_manager import StateSlotManager
 
 
 class Scheduler:
@@ -20,7 +21,12 @@ class Scheduler:
         self.max_num_seqs = config.max_num_seqs
         self.max_num_batched_tokens = config.max_num_batched_tokens
         self.eos = config.eos
-        self.block_manager = BlockManager(config.num_kvcache_blocks, config.kvcache_block_size)
+        # models with recurrent layers: a request also owns a state slot, and pages cannot be shared between requests
+        # (a cached page restores keys, not the state that goes with them)
+        stateful = bool(getattr(getattr(config, "hf_config", None), "is_hybrid", False))
+        self.block_manager = BlockManager(config.num_kvcache_blocks, config.kvcache_block_size,
+                                          enable_prefix_cache=not stateful)
+        self.state_manager = StateSlotManager(getattr(config, "num_state_slots", 0) or config.max_num_seqs) if stateful else None
         self.waiting: Deque[Sequence] = deque()
         self.running: Deque[Sequence] = deque()
 
@@ -95,8 +101,87 @@ class Scheduler:
             chosen.append(seq)
         return chosen
 
+    # ---- portions: chunked prefill beside decoding (models served token portion by token portion) -------------------
+    def admit(self, seq: Sequence) -> None:
+        """Make a request live: a state slot now, pages as its portions arrive (`reserve`)."""
+        if self.state_manager is not None:
+            self.state_manager.allocate(seq)
+        seq.status = SequenceStatus.RUNNING
+        if seq not in self.running:
+            self.running.append(seq)
+
+    def reserve(self, seq: Sequence, n_tokens: int) -> None:
+        """Pages for the first n_tokens tokens of a live request."""
+        if not self.block_manager.can_append(seq, n_tokens):
+            raise RuntimeError("out of KV cache blocks")
+        self.block_manager.ensure(seq, n_tokens)
+
+    def release(self, seq: Sequence) -> None:
+        """Hand back what a live request holds (pages and state slot)."""
+        self.block_manager.deallocate(seq)
+        if self.state_manager is not None:
+            self.state_manager.deallocate(seq)
+        if seq in self.running:
+            self.running.remove(seq)
+
+    def schedule_portions(self) -> List[Tuple[Sequence, int]]:
+        """One mixed step: every live request gets its next tokens (one decoded token, or the next portion of its
+        prompt), then waiting requests are admitted while slots, pages and the token budget last.  A request's
+        `num_cached_tokens` counts the tokens already run through the model."""
+        portions: List[Tuple[Sequence, int]] = []
+        budget = self.max_num_batched_tokens
+        for seq in list(self.running):
+            if budget <= 0 or len(portions) >= self.max_num_seqs:
+                break
+            if seq not in self.running:                      # preempted below
+                continue
+            n = min(len(seq) - seq.num_cached_tokens, budget)
+            evicted = False
+            while not self.block_manager.can_append(seq, seq.num_cached_tokens + n):
+                victim = self.running[-1]
+                self.preempt(victim)
+                portions = [(s, k) for s, k in portions if s is not victim]
+                if victim is seq:
+                    evicted = True
+                    break
+            if evicted:
+                continue
+            self.block_manager.ensure(seq, seq.num_cached_tokens + n)
+            portions.append((seq, n))
+            budget -= n
+        while self.waiting and budget > 0 and len(portions) < self.max_num_seqs:
+            seq = self.waiting[0]
+            if self.state_manager is not None and not self.state_manager.can_allocate():
+                break
+            n = min(len(seq), budget)
+            if len(self.block_manager.free_block_ids) < self.block_manager.blocks_for(n) + 1:
+                break
+            self.waiting.popleft()
+            self.admit(seq)
+            self.block_manager.ensure(seq, n)
+            portions.append((seq, n))
+            budget -= n
+        if not portions:
+            raise AssertionError("nothing can be scheduled: the KV cache / token budget cannot hold a single request")
+        return portions
+
+    def postprocess_portions(self, portions: Seq[Tuple[Sequence, int]], token_ids: Seq) -> None:
+        """token_ids[i] is the token sampled after portion i, or None while its prompt is still being fed."""
+        for (seq, n), tok in zip(portions, token_ids):
+            seq.num_cached_tokens += n
+            if tok is None:
+                continue
+            seq.append_token(tok)
+            hit_eos = tok == self.eos and not seq.ignore_eos
+            if hit_eos or seq.num_completion_tokens >= seq.max_tokens:
+                self._retire(seq)
+
     def preempt(self, seq: Sequence) -> None:
         self.block_manager.deallocate(seq)
+        if self.state_manager is not None:
+            self.state_manager.deallocate(seq)
+        if seq in self.running:
+            self.running.remove(seq)
         seq.status = SequenceStatus.WAITING
         self.waiting.appendleft(seq)
 
@@ -104,6 +189,8 @@ class Scheduler:
     def _retire(self, seq: Sequence) -> None:
         seq.status = SequenceStatus.FINISHED
         self.block_manager.deallocate(seq)
+        if self.state_manager is not None:
+            self.state_manager.deallocate(seq)
         self.running.remove(seq)
 
     def postprocess(self, seqs: Seq[Sequence], token_ids: Seq[int]) -> None:

@@ -38,6 +38,7 @@ class Sequence:
         self.last_token = self.token_ids[-1]
         self.num_cached_tokens = 0
         self.block_table: List[int] = []
+        self.state_slot = -1              # recurrent-state slot (models with stateful layers)
         # per-request sampling / decoding knobs
         self.sampling_params = sp
         self.temperature, self.max_tokens, self.ignore_eos = sp.temperature, sp.max_tokens, sp.ignore_eos
