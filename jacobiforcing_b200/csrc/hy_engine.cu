@@ -8,12 +8,14 @@
 #include <string.h>
 
 #include <algorithm>
+#include <type_traits>
 #include <map>
 #include <string>
 #include <vector>
 
 #include "../../include/jacobi_hybrid.h"
 #include "hy_kernels.cuh"
+#include "hy_gemm.cuh"
 
 namespace hy {
 
@@ -38,6 +40,8 @@ struct LayerW {
   void* conv_qkv = nullptr; void* w_a2 = nullptr; void* w_g2 = nullptr; void* A_log = nullptr; void* dt_bias = nullptr;
   void* norm_w = nullptr;                                                        // delta
   void* cache = nullptr;                                                         // key pages of this layer
+  // the same matrices as swizzled 128 x 64 tiles for the tensor-core product (bf16 build)
+  void* w_in_t = nullptr; void* w_out_t = nullptr; void* w_x_t = nullptr; void* w_a2_t = nullptr; void* w_g2_t = nullptr;
   float* conv_state = nullptr; float* conv_state2 = nullptr; float* rec_state = nullptr;
 };
 
@@ -51,7 +55,8 @@ struct hy_engine {
   std::vector<hy_layer_cfg> lc;
   std::map<std::string, HostTensor> host;
   std::vector<LayerW> lw;
-  void* embed = nullptr; void* final_norm = nullptr; void* head = nullptr; float* inv_freq = nullptr;
+  void* embed = nullptr; void* final_norm = nullptr; void* head = nullptr; void* head_t = nullptr; float* inv_freq = nullptr;
+  int* err_d = nullptr; int* err_h = nullptr;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::string err;
@@ -137,6 +142,7 @@ extern "C" void hy_destroy(hy_handle h) {
   cudaStreamSynchronize(h->stream);
   for (void* p : h->allocs) cudaFree(p);
   if (h->meta_h) cudaFreeHost(h->meta_h);
+  if (h->err_h) cudaFreeHost(h->err_h);
   cudaEventDestroy(h->ev0);
   cudaEventDestroy(h->ev1);
   cudaStreamDestroy(h->stream);
@@ -211,6 +217,15 @@ struct Builder {
     }
     return d;
   }
+  void* up_tiled(const std::vector<float>& v, int N, int K) {
+    if (rc != HY_OK || h->m.dtype != HY_DTYPE_BF16) return nullptr;
+    std::vector<uint16_t> t;
+    pack_tiles(v.data(), N, K, t);
+    void* d = nullptr;
+    if (dev_alloc(h, &d, t.size() * 2, &h->bytes_w) != HY_OK) { rc = HY_ERR_CUDA; return nullptr; }
+    cudaMemcpy(d, t.data(), t.size() * 2, cudaMemcpyHostToDevice);
+    return d;
+  }
   float* up_f32(const std::vector<float>& v) {
     void* d = nullptr;
     if (rc != HY_OK) return nullptr;
@@ -234,7 +249,7 @@ extern "C" int hy_finalize(hy_handle h) {
   const hy_runtime_cfg& rt = h->rt;
   if (auto t = B.get("embed", V, W)) h->embed = B.up(t->v);
   if (auto t = B.get("final.norm", W, -1)) h->final_norm = B.up(t->v);
-  if (auto t = B.get("head", V, W)) h->head = B.up(t->v);
+  if (auto t = B.get("head", V, W)) { h->head = B.up(t->v); h->head_t = B.up_tiled(t->v, V, W); }
   {
     std::vector<float> f((W + 1) / 2);
     for (size_t i = 0; i < f.size(); ++i) f[i] = (float)pow(10000.0, -2.0 * (double)i / (double)W);
@@ -266,7 +281,7 @@ extern "C" int hy_finalize(hy_handle h) {
       if (auto t = B.get(a + "sink", c.a_heads, -1)) L.sink = B.up(t->v);
       if (auto t = B.get(s + "conv", I, c.s_conv)) L.conv_x = B.up(t->v);
       if (auto t = B.get(s + "conv.b", I, -1)) L.conv_xb = B.up(t->v);
-      if (auto t = B.get(s + "x", R + 2 * N, I)) L.w_x = B.up(t->v);
+      if (auto t = B.get(s + "x", R + 2 * N, I)) { L.w_x = B.up(t->v); L.w_x_t = B.up_tiled(t->v, R + 2 * N, I); }
       if (auto t = B.get(s + "dt", I, R)) L.w_dt = B.up(t->v);
       if (auto t = B.get(s + "dt.b", I, -1)) L.dt_b = B.up(t->v);
       if (auto t = B.get(s + "A_log", I, N)) {
@@ -300,8 +315,8 @@ extern "C" int hy_finalize(hy_handle h) {
       stack_rows(cw, B.get(d + "k.conv", nq, c.d_conv));
       stack_rows(cw, B.get(d + "v.conv", nv, c.d_conv));
       L.conv_qkv = B.up(cw);
-      if (auto t = B.get(d + "a2", c.d_heads * c.d_dim, c.d_low_a)) L.w_a2 = B.up(t->v);
-      if (auto t = B.get(d + "g2", nv, c.d_low_g)) L.w_g2 = B.up(t->v);
+      if (auto t = B.get(d + "a2", c.d_heads * c.d_dim, c.d_low_a)) { L.w_a2 = B.up(t->v); L.w_a2_t = B.up_tiled(t->v, c.d_heads * c.d_dim, c.d_low_a); }
+      if (auto t = B.get(d + "g2", nv, c.d_low_g)) { L.w_g2 = B.up(t->v); L.w_g2_t = B.up_tiled(t->v, nv, c.d_low_g); }
       if (auto t = B.get(d + "A_log", c.d_heads, -1)) L.A_log = B.up_f32(t->v);
       if (auto t = B.get(d + "dt_bias", c.d_heads * c.d_dim, -1)) L.dt_bias = B.up_f32(t->v);
       if (auto t = B.get(d + "norm", c.d_vdim, -1)) L.norm_w = B.up_f32(t->v);
@@ -322,6 +337,7 @@ extern "C" int hy_finalize(hy_handle h) {
     if (B.rc != HY_OK) break;
     L.n_in = n_in;
     L.w_in = B.up(win);
+    L.w_in_t = B.up_tiled(win, n_in, W);
     int k_out = 0;
     for (auto t : outs) k_out += (int)t->cols();
     L.k_out = k_out;
@@ -333,6 +349,7 @@ extern "C" int hy_finalize(hy_handle h) {
       off += kc;
     }
     L.w_out = B.up(wout);
+    L.w_out_t = B.up_tiled(wout, W, k_out);
     max_in = std::max(max_in, L.c_up);
     max_out = std::max(max_out, k_out);
   }
@@ -357,6 +374,10 @@ extern "C" int hy_finalize(hy_handle h) {
   h->meta_words = 3 * T + 3 * (size_t)rt.max_step_entries + 1 + (size_t)rt.max_step_entries * rt.max_pages_per_seq + mw;
   if (dev_alloc(h, (void**)&h->meta_d, h->meta_words * 4, &h->bytes_ws)) return HY_ERR_CUDA;
   HY_CUDA(cudaMallocHost((void**)&h->meta_h, h->meta_words * 4));
+  if (dev_alloc(h, (void**)&h->err_d, 4, &h->bytes_ws)) return HY_ERR_CUDA;
+  HY_CUDA(cudaMemset(h->err_d, 0, 4));
+  HY_CUDA(cudaMallocHost((void**)&h->err_h, 4));
+  *h->err_h = 0;
   HY_CUDA(cudaDeviceSynchronize());
   h->finalized = true;
   return HY_OK;
@@ -366,9 +387,28 @@ extern "C" int hy_finalize(hy_handle h) {
 namespace {
 
 template <typename TA, typename TW, typename TO>
-int gemm(hy_engine* h, const TA* A, int lda, const TW* Wt, int ldw, int T, int N, int K, GemmOut o) {
+int gemm(hy_engine* h, const TA* A, int lda, const TW* Wt, int ldw, int T, int N, int K, GemmOut o,
+         const void* tiled = nullptr) {
   if (T <= 0 || N <= 0) return HY_OK;
   if (o.alpha == 0.0f) o.alpha = 1.0f;
+  if constexpr (std::is_same<TA, bf16>::value && std::is_same<TW, bf16>::value) {
+    if (tiled && T > 8 && K % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0) {
+      static bool attr_set = false;
+      if (!attr_set) {
+        cudaFuncSetAttribute(gemm_tc_kernel<TO, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(128));
+        cudaFuncSetAttribute(gemm_tc_kernel<TO, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(256));
+        attr_set = true;
+      }
+      if (T > 128)
+        gemm_tc_kernel<TO, 256><<<dim3((N + 127) / 128, (T + 255) / 256), 192, tc_smem_bytes(256), h->stream>>>(
+            A, lda, (const bf16*)tiled, T, N, K, o, h->err_d);
+      else
+        gemm_tc_kernel<TO, 128><<<dim3((N + 127) / 128, (T + 127) / 128), 192, tc_smem_bytes(128), h->stream>>>(
+            A, lda, (const bf16*)tiled, T, N, K, o, h->err_d);
+      h->launches++;
+      return HY_OK;
+    }
+  }
   if (T <= 8 && (size_t)8 * K * 4 <= 160 * 1024) {
     const int nw = 8;
     const int blocks = std::min((N + nw - 1) / nw, 148 * 8);
@@ -408,7 +448,7 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
     // every projection that reads the normed input, in one product; the feed-forward's hidden part leaves activated,
     // straight into the operand of the merged output projection
     GemmOut o_in{pin, h->ld_pin, L.c_up, cat + L.o_ff, h->ld_cat, 1, nullptr, 0, 1.0f};
-    gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, o_in);
+    gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, o_in, L.w_in_t);
     if (c.mixer == HY_MIX_ATTN_SCAN) {
       const int nq = c.a_heads * c.a_dim, nk = c.a_kv_heads * c.a_dim, I = c.s_inner, N = c.s_state, R = c.s_dt_rank;
       // attention side: conv over q | k, keys into their pages, attention over the pages
@@ -425,7 +465,7 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
                                                                    (const WT*)L.conv_xb, 1, L.conv_state2, cv, h->ld_cv);
       conv_tail_kernel<AT><<<dim3((I + 127) / 128, E), 128, 0, s>>>(b, pin, h->ld_pin, L.c_x, I, c.s_conv, L.conv_state2);
       h->launches += 2;
-      gemm<AT, WT, float>(h, cv, h->ld_cv, (const WT*)L.w_x, I, T, R + 2 * N, I, to_buf(h->f1, h->ld_f1));
+      gemm<AT, WT, float>(h, cv, h->ld_cv, (const WT*)L.w_x, I, T, R + 2 * N, I, to_buf(h->f1, h->ld_f1), L.w_x_t);
       gemm<float, WT, float>(h, h->f1, h->ld_f1, (const WT*)L.w_dt, R, T, I, R, to_buf(h->f2, h->ld_f2));
       {
         int nper = N <= 128 ? 4 : 8;
@@ -447,8 +487,9 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
       conv_tail_kernel<AT><<<dim3((C + 127) / 128, E), 128, 0, s>>>(b, pin, h->ld_pin, L.c_q, C, c.d_conv, L.conv_state);
       h->launches += 2;
       gemm<AT, WT, float>(h, pin + L.c_a1, h->ld_pin, (const WT*)L.w_a2, c.d_low_a, T, c.d_heads * c.d_dim, c.d_low_a,
-                          to_buf(h->f1, h->ld_f1));
-      gemm<AT, WT, float>(h, pin + L.c_g1, h->ld_pin, (const WT*)L.w_g2, c.d_low_g, T, nv, c.d_low_g, to_buf(h->f2, h->ld_f2));
+                          to_buf(h->f1, h->ld_f1), L.w_a2_t);
+      gemm<AT, WT, float>(h, pin + L.c_g1, h->ld_pin, (const WT*)L.w_g2, c.d_low_g, T, nv, c.d_low_g, to_buf(h->f2, h->ld_f2),
+                          L.w_g2_t);
       const int threads = ((std::max(c.d_dim, c.d_vdim) + 31) / 32) * 32;
       const size_t smem = ((size_t)c.d_dim * c.d_vdim + 3 * c.d_dim + 40) * 4;
       cudaFuncSetAttribute(delta_kernel<AT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
@@ -461,7 +502,7 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
     (void)ff;
     // merged output projections, added to the residual stream
     GemmOut o_out{nullptr, 0, 0, nullptr, 0, 0, h->x, W, 1.0f};
-    gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_out, L.k_out, T, W, L.k_out, o_out);
+    gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_out, L.k_out, T, W, L.k_out, o_out, L.w_out_t);
     if (layers_out) {
       cudaMemcpyAsync(layers_out + li * (size_t)T * W, h->x, (size_t)T * W * 4, cudaMemcpyDeviceToHost, s);
     }
@@ -471,7 +512,7 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
     h->launches++;
     GemmOut o = to_buf(h->logits, h->m.vocab);
     o.alpha = h->m.logit_scale;
-    gemm<AT, WT, float>(h, (const AT*)h->hw, W, (const WT*)h->head, W, n_want, h->m.vocab, W, o);
+    gemm<AT, WT, float>(h, (const AT*)h->hw, W, (const WT*)h->head, W, n_want, h->m.vocab, W, o, h->head_t);
   }
   return HY_OK;
 }
@@ -544,8 +585,14 @@ extern "C" int hy_step(hy_handle h, int32_t n_entries, const int32_t* tokens, co
   HY_CUDA(cudaEventRecord(h->ev1, h->stream));
   if (n_want > 0 && logits_out)
     HY_CUDA(cudaMemcpyAsync(logits_out, h->logits, (size_t)n_want * h->m.vocab * 4, cudaMemcpyDeviceToHost, h->stream));
+  HY_CUDA(cudaMemcpyAsync(h->err_h, h->err_d, 4, cudaMemcpyDeviceToHost, h->stream));
   HY_CUDA(cudaStreamSynchronize(h->stream));
   HY_CUDA(cudaGetLastError());
+  if (*h->err_h) {
+    *h->err_h = 0;
+    cudaMemset(h->err_d, 0, 4);
+    return fail(h, HY_ERR_CUDA, "a wait inside the tensor-core matrix product ran out (pipeline stalled)");
+  }
   cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1);
   return HY_OK;
 }
