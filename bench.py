@@ -455,6 +455,31 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         dist.destroy_process_group()
 
 
+def run_compare_hybrid(args):
+    """Option --compare-hybrid: the layered hybrid decoder beside the closest existing model (Qwen2) at equal width, depth
+    and feed-forward size; device times from CUDA events, three warm-up passes, weights + activations larger than L2."""
+    import __graft_entry__ as g
+    g.build()
+    from jacobiforcing_b200 import hybrid_bench as hb
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp = json.load(f)
+        peaks = {"hbm_gbs": float(mp["hbm_gbs"]), "bf16_tflops": float(mp["bf16_tflops"]), "source": "measured"}
+    except Exception:
+        peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    mon = ClockSampler(0)
+    mon.start()
+    res = []
+    for size in args.compare_hybrid.split(","):
+        row = {"size": size}
+        row["hybrid"] = hb.run_hybrid(size, args.hybrid_prompt, args.hybrid_decode_steps, [1, 8], peaks)
+        row["qwen2"] = hb.run_qwen2(size, args.hybrid_prompt, args.hybrid_decode_steps, [1, 8], peaks)
+        res.append(row)
+    clocks = mon.stop()
+    print(json.dumps({"metric": "hybrid_vs_qwen2_throughput", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+                      "peaks": peaks, "clocks": clocks, "results": res}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -479,7 +504,15 @@ def main():
     ap.add_argument("--tp-attn", default="auto", choices=["auto", "shard", "replicate"],
                     help="attention block under tensor parallelism: sharded by heads (must divide tp), replicated on "
                          "every rank (MLP-only TP, one exchange per block), or auto = shard when the heads divide")
+    ap.add_argument("--compare-hybrid", default="", metavar="SIZES",
+                    help="instead of the headline workload: prefill / decode throughput of the layered hybrid decoder "
+                         "(Kinetar) beside Qwen2 at equal size, e.g. w1024,w2048,w4096 (one JSON line)")
+    ap.add_argument("--hybrid-prompt", type=int, default=4096)
+    ap.add_argument("--hybrid-decode-steps", type=int, default=35)
     args = ap.parse_args()
+    if args.compare_hybrid:
+        run_compare_hybrid(args)
+        return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3                                  # timing rule: at least three warm-up steps
     rank = int(os.environ.get("RANK", "0"))

@@ -84,6 +84,12 @@ float hy_last_step_ms(hy_handle h);
 /* Bytes of device memory held: weights, cache pages, state slots, workspace. */
 int hy_memory_info(hy_handle h, int64_t* weights, int64_t* cache, int64_t* state, int64_t* workspace);
 
+/* Device time per group of kernels, summed over the steps since hy_profile_enable(h, 1): ms[HY_PROFILE_CATEGORIES]. */
+enum { HY_PROF_NORM = 0, HY_PROF_GEMM_IN = 1, HY_PROF_CONV = 2, HY_PROF_ATTN = 3, HY_PROF_SMALL_GEMM = 4, HY_PROF_SCAN = 5,
+       HY_PROF_DELTA = 6, HY_PROF_GEMM_OUT = 7, HY_PROF_HEAD = 8, HY_PROFILE_CATEGORIES = 9 };
+int hy_profile_enable(hy_handle h, int32_t on);
+int hy_profile_read(hy_handle h, float* ms);
+
 #ifdef __cplusplus
 }
 #endif

@@ -10,11 +10,12 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libjf_hybrid.so")
-SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("hy_engine.cu", "hy_kernels.cuh", "hy_gemm.cuh", "jf_ptx.cuh")] + [
+SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("hy_engine.cu", "hy_kernels.cuh", "hy_gemm.cuh", "hy_attn.cuh", "jf_ptx.cuh")] + [
     os.path.join(ROOT, "include", "jacobi_hybrid.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]
 EXPORTS = ["hy_create", "hy_destroy", "hy_last_error", "hy_load_tensor", "hy_finalize", "hy_step", "hy_launch_count",
-           "hy_last_step_ms", "hy_memory_info"]
+           "hy_last_step_ms", "hy_memory_info", "hy_profile_enable", "hy_profile_read"]
+PROFILE_CATEGORIES = ("norm_embed", "gemm_in", "conv_cache", "attention", "small_gemm", "scan", "delta", "gemm_out", "head")
 HY_OK, HY_ERR_INVALID, HY_ERR_CUDA, HY_ERR_CAPACITY, HY_ERR_UNSUPPORTED = 0, -1, -2, -3, -4
 
 
@@ -86,7 +87,9 @@ def load() -> C.CDLL:
     lib.hy_last_step_ms.argtypes = [vp]
     lib.hy_last_step_ms.restype = C.c_float
     lib.hy_memory_info.argtypes = [vp, i64p, i64p, i64p, i64p]
-    for n in ("hy_create", "hy_load_tensor", "hy_finalize", "hy_step", "hy_memory_info"):
+    lib.hy_profile_enable.argtypes = [vp, i32]
+    lib.hy_profile_read.argtypes = [vp, fp]
+    for n in ("hy_profile_enable", "hy_profile_read", "hy_create", "hy_load_tensor", "hy_finalize", "hy_step", "hy_memory_info"):
         getattr(lib, n).restype = C.c_int
     _lib = lib
     return lib

@@ -16,6 +16,7 @@
 #include "../../include/jacobi_hybrid.h"
 #include "hy_kernels.cuh"
 #include "hy_gemm.cuh"
+#include "hy_attn.cuh"
 
 namespace hy {
 
@@ -57,6 +58,16 @@ struct hy_engine {
   std::vector<LayerW> lw;
   void* embed = nullptr; void* final_norm = nullptr; void* head = nullptr; void* head_t = nullptr; float* inv_freq = nullptr;
   int* err_d = nullptr; int* err_h = nullptr;
+  // per-category device times (hy_profile_enable): event pairs recorded around groups of launches
+  bool prof_on = false;
+  float prof_ms[HY_PROFILE_CATEGORIES] = {};
+  std::vector<cudaEvent_t> ev_pool;
+  struct ProfRec { int cat; cudaEvent_t a, b; };
+  std::vector<ProfRec> prof_list;
+  cudaEvent_t get_event() {
+    if (!ev_pool.empty()) { cudaEvent_t e = ev_pool.back(); ev_pool.pop_back(); return e; }
+    cudaEvent_t e; cudaEventCreate(&e); return e;
+  }
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::string err;
@@ -71,6 +82,11 @@ struct hy_engine {
   float* temp_d = nullptr;
   int ld_pin = 0, ld_cat = 0, ld_cv = 0, ld_f1 = 0, ld_f2 = 0;
   int* meta_d = nullptr; int* meta_h = nullptr; size_t meta_words = 0;
+  // tensor-core attention: work units of the step (per head layout), partial results per (row, key split)
+  AttnUnit* units_d = nullptr; AttnUnit* units_h = nullptr; size_t units_cap = 0; int units_n = 0;
+  int units_H = 0, units_G = 0, units_split = 0, units_ns = 0;
+  float* part_o = nullptr; float* part_ml = nullptr; size_t part_rows = 0;
+  const int32_t* step_start = nullptr; const int32_t* step_pos0 = nullptr;     // host views of the running step
   size_t esz() const { return m.dtype == HY_DTYPE_F32 ? 4 : 2; }
 };
 
@@ -82,6 +98,16 @@ struct hy_engine {
       return HY_ERR_CUDA;                                                                               \
     }                                                                                                   \
   } while (0)
+
+struct ProfScope {
+  hy_engine* h; int cat; cudaEvent_t a{}, b{};
+  ProfScope(hy_engine* h_, int cat_) : h(h_), cat(cat_) {
+    if (h->prof_on) { a = h->get_event(); b = h->get_event(); cudaEventRecord(a, h->stream); }
+  }
+  ~ProfScope() {
+    if (h->prof_on) { cudaEventRecord(b, h->stream); h->prof_list.push_back({cat, a, b}); }
+  }
+};
 
 static int fail(hy_engine* h, int code, const std::string& msg) {
   h->err = msg;
@@ -142,6 +168,7 @@ extern "C" void hy_destroy(hy_handle h) {
   cudaStreamSynchronize(h->stream);
   for (void* p : h->allocs) cudaFree(p);
   if (h->meta_h) cudaFreeHost(h->meta_h);
+  if (h->units_h) cudaFreeHost(h->units_h);
   if (h->err_h) cudaFreeHost(h->err_h);
   cudaEventDestroy(h->ev0);
   cudaEventDestroy(h->ev1);
@@ -152,6 +179,17 @@ extern "C" void hy_destroy(hy_handle h) {
 extern "C" const char* hy_last_error(hy_handle h) { return h ? h->err.c_str() : g_create_err.c_str(); }
 extern "C" int64_t hy_launch_count(hy_handle h) { return h ? h->launches : 0; }
 extern "C" float hy_last_step_ms(hy_handle h) { return h ? h->last_ms : 0.0f; }
+extern "C" int hy_profile_enable(hy_handle h, int32_t on) {
+  if (!h) return HY_ERR_INVALID;
+  h->prof_on = on != 0;
+  for (float& v : h->prof_ms) v = 0.0f;
+  return HY_OK;
+}
+extern "C" int hy_profile_read(hy_handle h, float* ms) {
+  if (!h || !ms) return HY_ERR_INVALID;
+  for (int i = 0; i < HY_PROFILE_CATEGORIES; ++i) ms[i] = h->prof_ms[i];
+  return HY_OK;
+}
 extern "C" int hy_memory_info(hy_handle h, int64_t* w, int64_t* c, int64_t* s, int64_t* ws) {
   if (!h) return HY_ERR_INVALID;
   if (w) *w = h->bytes_w;
@@ -374,6 +412,19 @@ extern "C" int hy_finalize(hy_handle h) {
   h->meta_words = 3 * T + 3 * (size_t)rt.max_step_entries + 1 + (size_t)rt.max_step_entries * rt.max_pages_per_seq + mw;
   if (dev_alloc(h, (void**)&h->meta_d, h->meta_words * 4, &h->bytes_ws)) return HY_ERR_CUDA;
   HY_CUDA(cudaMallocHost((void**)&h->meta_h, h->meta_words * 4));
+  if (h->m.dtype == HY_DTYPE_BF16) {
+    int maxH = 0, maxG = 0, maxD = 0;
+    for (auto& c : h->lc)
+      if (c.mixer == HY_MIX_ATTN_SCAN) { maxH = std::max(maxH, c.a_heads); maxG = std::max(maxG, c.a_kv_heads); maxD = std::max(maxD, c.a_dim); }
+    if (maxH > 0) {
+      h->part_rows = std::max<size_t>(T * maxH, 4096);
+      h->units_cap = h->part_rows / 64 + (size_t)rt.max_step_entries * maxG * 257 + 64;
+      if (dev_alloc(h, (void**)&h->part_o, h->part_rows * maxD * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->part_ml, h->part_rows * 2 * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->units_d, h->units_cap * sizeof(AttnUnit), &h->bytes_ws)) return HY_ERR_CUDA;
+      HY_CUDA(cudaMallocHost((void**)&h->units_h, h->units_cap * sizeof(AttnUnit)));
+    }
+  }
   if (dev_alloc(h, (void**)&h->err_d, 4, &h->bytes_ws)) return HY_ERR_CUDA;
   HY_CUDA(cudaMemset(h->err_d, 0, 4));
   HY_CUDA(cudaMallocHost((void**)&h->err_h, 4));
@@ -392,7 +443,9 @@ int gemm(hy_engine* h, const TA* A, int lda, const TW* Wt, int ldw, int T, int N
   if (T <= 0 || N <= 0) return HY_OK;
   if (o.alpha == 0.0f) o.alpha = 1.0f;
   if constexpr (std::is_same<TA, bf16>::value && std::is_same<TW, bf16>::value) {
-    if (tiled && T > 8 && K % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0) {
+    const size_t rb = (size_t)((K + 7) / 8 * 8) * 2;
+    const bool rows_fit = T <= 8 && rb * (T == 1 ? 1 : T == 2 ? 2 : T <= 4 ? 4 : 8) <= 200 * 1024;
+    if (tiled && !rows_fit && K % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0) {
       static bool attr_set = false;
       if (!attr_set) {
         cudaFuncSetAttribute(gemm_tc_kernel<TO, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(128));
@@ -409,17 +462,23 @@ int gemm(hy_engine* h, const TA* A, int lda, const TW* Wt, int ldw, int T, int N
       return HY_OK;
     }
   }
-  if (T <= 8 && (size_t)8 * K * 4 <= 160 * 1024) {
-    const int nw = 8;
-    const int blocks = std::min((N + nw - 1) / nw, 148 * 8);
+  constexpr int VECW = 16 / (int)sizeof(TW);
+  const size_t row_bytes = (size_t)((K + VECW - 1) / VECW * VECW) * sizeof(TA);
+  const int want_rows = T == 1 ? 1 : T == 2 ? 2 : T <= 4 ? 4 : 8;
+  if (T <= 8 && row_bytes * want_rows <= 200 * 1024) {
+    int ksplit = 1;
+    while (ksplit < 8 && (long long)N * ksplit < 148LL * 32 && K / (ksplit * 2) >= 512) ksplit *= 2;
+    const int cpb = 8 / ksplit;
+    const int blocks = std::min((N + cpb - 1) / cpb, 148 * 16);
+    const int fit = (int)((200 * 1024) / row_bytes);
     auto launch = [&](auto kern, int rows) {
-      const size_t smem = (size_t)rows * K * 4;
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-      kern<<<dim3(blocks, (T + rows - 1) / rows), 256, smem, h->stream>>>(A, lda, Wt, ldw, T, N, K, o);
+      const size_t smem = (size_t)rows * row_bytes;
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      kern<<<dim3(blocks, (T + rows - 1) / rows), 256, smem, h->stream>>>(A, lda, Wt, ldw, T, N, K, ksplit, o);
     };
-    if (T == 1) launch(gemm_rows_kernel<TA, TW, TO, 1>, 1);
-    else if (T == 2) launch(gemm_rows_kernel<TA, TW, TO, 2>, 2);
-    else if (T <= 4) launch(gemm_rows_kernel<TA, TW, TO, 4>, 4);
+    if (T == 1 || fit < 2) launch(gemm_rows_kernel<TA, TW, TO, 1>, 1);
+    else if (T == 2 || fit < 4) launch(gemm_rows_kernel<TA, TW, TO, 2>, 2);
+    else if (T <= 4 || fit < 8) launch(gemm_rows_kernel<TA, TW, TO, 4>, 4);
     else launch(gemm_rows_kernel<TA, TW, TO, 8>, 8);
   } else {
     gemm_simt_kernel<TA, TW, TO><<<dim3((N + 63) / 64, (T + 63) / 64), 256, 0, h->stream>>>(A, lda, Wt, ldw, T, N, K, o);
@@ -430,6 +489,36 @@ int gemm(hy_engine* h, const TA* A, int lda, const TW* Wt, int ldw, int T, int N
 
 GemmOut to_buf(void* out, int ld) { return GemmOut{out, ld, 1 << 30, nullptr, 0, 0, nullptr, 0, 1.0f}; }
 
+// Work units of the tensor-core attention for this step and this head layout; returns false when the layout does not fit
+// the kernel (the SIMT kernel serves it then).
+bool attn_units(hy_engine* h, int E, int T, int H, int G) {
+  const int R = H / G;
+  if (R > 64 || 64 % R) return false;
+  if (h->units_n > 0 && h->units_H == H && h->units_G == G) return true;
+  int maxctx = 1;
+  for (int e = 0; e < E; ++e) maxctx = std::max(maxctx, h->step_pos0[e] + h->step_start[e + 1] - h->step_start[e]);
+  const int ns_cap = (int)std::max<size_t>(1, h->part_rows / ((size_t)T * H));
+  int ns = std::min(std::min((maxctx + 255) / 256, ns_cap), 256);
+  const int split = ((maxctx + ns - 1) / ns + 63) / 64 * 64;
+  ns = (maxctx + split - 1) / split;
+  if (h->units_n > 0) cudaStreamSynchronize(h->stream);        // another layout earlier in this step still reads the list
+  size_t n = 0;
+  for (int e = 0; e < E; ++e) {
+    const int cnt = h->step_start[e + 1] - h->step_start[e], pos0 = h->step_pos0[e], rows = cnt * R;
+    for (int g = 0; g < G; ++g)
+      for (int row0 = 0; row0 < rows; row0 += 64) {
+        const int last_pos = pos0 + std::min(row0 + 63, rows - 1) / R;
+        for (int sp = 0; sp * split <= last_pos; ++sp) {
+          if (n >= h->units_cap) return false;
+          h->units_h[n++] = AttnUnit{e, g, row0, sp};
+        }
+      }
+  }
+  cudaMemcpyAsync(h->units_d, h->units_h, n * sizeof(AttnUnit), cudaMemcpyHostToDevice, h->stream);
+  h->units_n = (int)n; h->units_H = H; h->units_G = G; h->units_split = split; h->units_ns = ns;
+  return true;
+}
+
 template <typename AT>
 int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float* layers_out) {
   typedef AT WT;
@@ -437,77 +526,148 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
   const float eps = h->m.norm_eps;
   cudaStream_t s = h->stream;
   AT* hb = (AT*)h->hbuf; AT* pin = (AT*)h->pin; AT* cat = (AT*)h->cat; AT* cv = (AT*)h->cv;
-  embed_kernel<WT><<<T, 128, 0, s>>>(b, (const WT*)h->embed, h->inv_freq, h->m.emb_scale, W, h->x);
-  h->launches++;
+  {
+    ProfScope ps(h, HY_PROF_NORM);
+    embed_kernel<WT><<<T, 128, 0, s>>>(b, (const WT*)h->embed, h->inv_freq, h->m.emb_scale, W, h->x);
+    h->launches++;
+  }
   for (size_t li = 0; li < h->lc.size(); ++li) {
     const hy_layer_cfg& c = h->lc[li];
     const LayerW& L = h->lw[li];
     const int ff = c.ff_kind == HY_FF_NONE ? 0 : c.ff;
-    rmsnorm_kernel<WT, AT><<<T, 256, 0, s>>>(h->x, nullptr, (const WT*)L.norm1, eps, W, hb);
-    h->launches++;
+    {
+      ProfScope ps(h, HY_PROF_NORM);
+      rmsnorm_kernel<WT, AT><<<T, 256, 0, s>>>(h->x, nullptr, (const WT*)L.norm1, eps, W, hb);
+      h->launches++;
+    }
     // every projection that reads the normed input, in one product; the feed-forward's hidden part leaves activated,
     // straight into the operand of the merged output projection
     GemmOut o_in{pin, h->ld_pin, L.c_up, cat + L.o_ff, h->ld_cat, 1, nullptr, 0, 1.0f};
-    gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, o_in, L.w_in_t);
+    {
+      ProfScope ps(h, HY_PROF_GEMM_IN);
+      gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, o_in, L.w_in_t);
+    }
     if (c.mixer == HY_MIX_ATTN_SCAN) {
       const int nq = c.a_heads * c.a_dim, nk = c.a_kv_heads * c.a_dim, I = c.s_inner, N = c.s_state, R = c.s_dt_rank;
       // attention side: conv over q | k, keys into their pages, attention over the pages
+      {
+      ProfScope ps(h, HY_PROF_CONV);
       conv_kernel<AT, WT><<<dim3((nq + nk + 127) / 128, T), 128, 0, s>>>(b, pin, h->ld_pin, L.c_q, nq + nk, c.a_conv,
           (const WT*)L.conv_qk, (const WT*)nullptr, 0, L.conv_state, cv, h->ld_cv);
       conv_tail_kernel<AT><<<dim3((nq + nk + 127) / 128, E), 128, 0, s>>>(b, pin, h->ld_pin, L.c_q, nq + nk, c.a_conv, L.conv_state);
       cache_append_kernel<AT><<<T, 128, 0, s>>>(b, cv, h->ld_cv, nq, c.a_kv_heads, c.a_dim, (AT*)L.cache);
+      }
+      {
+      ProfScope ps(h, HY_PROF_ATTN);
+      bool tc = false;
+      if constexpr (std::is_same<AT, bf16>::value) {
+        if ((c.a_dim == 32 || c.a_dim == 64 || c.a_dim == 128) && h->part_o && attn_units(h, E, T, c.a_heads, c.a_kv_heads)) {
+          tc = true;
+#define HY_ATTN_ARGS b, h->units_d, cv, h->ld_cv, (const bf16*)L.cache, c.a_heads, c.a_kv_heads, c.a_scale, c.a_qt_coef, \
+          c.a_qt_every, h->units_split, h->units_ns, h->part_o, h->part_ml
+          if (c.a_dim == 32) attn_mma_kernel<32><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
+          else if (c.a_dim == 64) attn_mma_kernel<64><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
+          else attn_mma_kernel<128><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
+#undef HY_ATTN_ARGS
+          attn_combine_kernel<WT><<<T * c.a_heads, 64, 0, s>>>(b, h->part_o, h->part_ml, (const WT*)L.sink, pin + L.c_g, h->ld_pin,
+              c.a_heads, c.a_dim, h->units_split, h->units_ns, c.left_scale, cat + L.o_mix, h->ld_cat);
+          h->launches++;
+        }
+      }
+      if (!tc)
       attn_sink_kernel<AT, WT><<<(T * c.a_heads + 3) / 4, 128, 4 * c.a_dim * sizeof(float), s>>>(
           b, cv, h->ld_cv, (const AT*)L.cache, (const WT*)L.sink, pin + L.c_g, h->ld_pin, c.a_heads, c.a_kv_heads, c.a_dim,
           c.a_scale, c.a_qt_coef, c.a_qt_every, c.left_scale, cat + L.o_mix, h->ld_cat);
+      }
       h->launches += 4;
       // scan side
+      {
+      ProfScope ps(h, HY_PROF_CONV);
       conv_kernel<AT, WT><<<dim3((I + 127) / 128, T), 128, 0, s>>>(b, pin, h->ld_pin, L.c_x, I, c.s_conv, (const WT*)L.conv_x,
                                                                    (const WT*)L.conv_xb, 1, L.conv_state2, cv, h->ld_cv);
       conv_tail_kernel<AT><<<dim3((I + 127) / 128, E), 128, 0, s>>>(b, pin, h->ld_pin, L.c_x, I, c.s_conv, L.conv_state2);
+      }
       h->launches += 2;
+      {
+      ProfScope ps(h, HY_PROF_SMALL_GEMM);
       gemm<AT, WT, float>(h, cv, h->ld_cv, (const WT*)L.w_x, I, T, R + 2 * N, I, to_buf(h->f1, h->ld_f1), L.w_x_t);
       gemm<float, WT, float>(h, h->f1, h->ld_f1, (const WT*)L.w_dt, R, T, I, R, to_buf(h->f2, h->ld_f2));
+      }
       {
-        int nper = N <= 128 ? 4 : 8;
+        ProfScope ps(h, HY_PROF_SCAN);
+        const int nper = N <= 32 ? 1 : N <= 64 ? 2 : N <= 128 ? 4 : 8;
         int lanes = 1;
         while (lanes * nper < N) lanes <<= 1;
-        dim3 grid((I + 128 / lanes - 1) / (128 / lanes), E);
-        if (nper == 4)
-          scan_kernel<AT, WT, 4><<<grid, 128, 0, s>>>(b, cv, h->ld_cv, pin + L.c_z, h->ld_pin, h->f2, h->ld_f2, (const WT*)L.dt_b,
-              h->f1, h->ld_f1, R, R + N, L.A_neg, (const WT*)L.D, I, N, lanes, c.right_scale, L.rec_state, cat + L.o_scan, h->ld_cat);
-        else
-          scan_kernel<AT, WT, 8><<<grid, 128, 0, s>>>(b, cv, h->ld_cv, pin + L.c_z, h->ld_pin, h->f2, h->ld_f2, (const WT*)L.dt_b,
-              h->f1, h->ld_f1, R, R + N, L.A_neg, (const WT*)L.D, I, N, lanes, c.right_scale, L.rec_state, cat + L.o_scan, h->ld_cat);
+        const int per_block = 128 / lanes;
+        dim3 grid((I + per_block - 1) / per_block, E);
+        const size_t smem = (size_t)HY_SCAN_TB * (2 * N + 3 * per_block) * 4;
+#define HY_SCAN_ARGS b, cv, h->ld_cv, pin + L.c_z, h->ld_pin, h->f2, h->ld_f2, (const WT*)L.dt_b, h->f1, h->ld_f1, R, R + N, L.A_neg, \
+        (const WT*)L.D, I, N, lanes, c.right_scale, L.rec_state, cat + L.o_scan, h->ld_cat
+        if (nper == 1) scan_kernel<AT, WT, 1><<<grid, 128, smem, s>>>(HY_SCAN_ARGS);
+        else if (nper == 2) scan_kernel<AT, WT, 2><<<grid, 128, smem, s>>>(HY_SCAN_ARGS);
+        else if (nper == 4) scan_kernel<AT, WT, 4><<<grid, 128, smem, s>>>(HY_SCAN_ARGS);
+        else scan_kernel<AT, WT, 8><<<grid, 128, smem, s>>>(HY_SCAN_ARGS);
+#undef HY_SCAN_ARGS
         h->launches++;
       }
     } else {
       const int nq = c.d_kv_heads * c.d_dim, nv = c.d_heads * c.d_vdim, C = 2 * nq + nv;
+      {
+      ProfScope ps(h, HY_PROF_CONV);
       conv_kernel<AT, WT><<<dim3((C + 127) / 128, T), 128, 0, s>>>(b, pin, h->ld_pin, L.c_q, C, c.d_conv, (const WT*)L.conv_qkv,
                                                                    (const WT*)nullptr, 1, L.conv_state, cv, h->ld_cv);
       conv_tail_kernel<AT><<<dim3((C + 127) / 128, E), 128, 0, s>>>(b, pin, h->ld_pin, L.c_q, C, c.d_conv, L.conv_state);
+      }
       h->launches += 2;
+      {
+      ProfScope ps(h, HY_PROF_SMALL_GEMM);
       gemm<AT, WT, float>(h, pin + L.c_a1, h->ld_pin, (const WT*)L.w_a2, c.d_low_a, T, c.d_heads * c.d_dim, c.d_low_a,
                           to_buf(h->f1, h->ld_f1), L.w_a2_t);
       gemm<AT, WT, float>(h, pin + L.c_g1, h->ld_pin, (const WT*)L.w_g2, c.d_low_g, T, nv, c.d_low_g, to_buf(h->f2, h->ld_f2),
                           L.w_g2_t);
+      }
+      ProfScope ps(h, HY_PROF_DELTA);
       const int threads = ((std::max(c.d_dim, c.d_vdim) + 31) / 32) * 32;
-      const size_t smem = ((size_t)c.d_dim * c.d_vdim + 3 * c.d_dim + 40) * 4;
-      cudaFuncSetAttribute(delta_kernel<AT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-      delta_kernel<AT, float><<<dim3(c.d_heads, E), threads, smem, s>>>(
-          b, cv, h->ld_cv, 0, nq, 2 * nq, pin, h->ld_pin, L.c_b, h->f1, h->ld_f1, h->f2, h->ld_f2, (const float*)L.A_log,
-          (const float*)L.dt_bias, (const float*)L.norm_w, c.d_heads, c.d_kv_heads, c.d_dim, c.d_vdim, eps, L.rec_state,
-          cat + L.o_mix, h->ld_cat);
+#define HY_DELTA_ARGS b, cv, h->ld_cv, 0, nq, 2 * nq, pin, h->ld_pin, L.c_b, h->f1, h->ld_f1, h->f2, h->ld_f2, \
+      (const float*)L.A_log, (const float*)L.dt_bias, (const float*)L.norm_w, c.d_heads, c.d_kv_heads, c.d_dim, c.d_vdim, eps, \
+      L.rec_state, cat + L.o_mix, h->ld_cat
+      static bool delta_attr = false;
+      if (!delta_attr) {
+        cudaFuncSetAttribute(delta_reg_kernel<AT, float, 32, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(delta_reg_kernel<AT, float, 64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(delta_reg_kernel<AT, float, 128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        delta_attr = true;
+      }
+      // one thread per value column, whole warps
+      const int nthr = std::max(((c.d_vdim + 31) / 32) * 32, 32);
+      auto dsm = [](int dr, int nt) { return (size_t)HY_DELTA_TB * (3 * dr + 3 * nt + 1) * 4; };
+      if (c.d_dim <= 32 && nthr <= 512)
+        delta_reg_kernel<AT, float, 32, 1><<<dim3(c.d_heads, E), nthr, dsm(32, nthr), s>>>(HY_DELTA_ARGS);
+      else if (c.d_dim <= 64 && nthr <= 256)
+        delta_reg_kernel<AT, float, 64, 1><<<dim3(c.d_heads, E), nthr, dsm(64, nthr), s>>>(HY_DELTA_ARGS);
+      else if (c.d_dim <= 128 && nthr <= 256)
+        delta_reg_kernel<AT, float, 128, 1><<<dim3(c.d_heads, E), nthr, dsm(128, nthr), s>>>(HY_DELTA_ARGS);
+      else {
+        const size_t smem = ((size_t)c.d_dim * c.d_vdim + 3 * c.d_dim + 40) * 4;
+        cudaFuncSetAttribute(delta_kernel<AT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        delta_kernel<AT, float><<<dim3(c.d_heads, E), threads, smem, s>>>(HY_DELTA_ARGS);
+      }
+#undef HY_DELTA_ARGS
       h->launches++;
     }
     (void)ff;
     // merged output projections, added to the residual stream
     GemmOut o_out{nullptr, 0, 0, nullptr, 0, 0, h->x, W, 1.0f};
-    gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_out, L.k_out, T, W, L.k_out, o_out, L.w_out_t);
+    {
+      ProfScope ps(h, HY_PROF_GEMM_OUT);
+      gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_out, L.k_out, T, W, L.k_out, o_out, L.w_out_t);
+    }
     if (layers_out) {
       cudaMemcpyAsync(layers_out + li * (size_t)T * W, h->x, (size_t)T * W * 4, cudaMemcpyDeviceToHost, s);
     }
   }
   if (n_want > 0) {
+    ProfScope ps(h, HY_PROF_HEAD);
     rmsnorm_kernel<WT, AT><<<n_want, 256, 0, s>>>(h->x, want_d, (const WT*)h->final_norm, eps, W, (AT*)h->hw);
     h->launches++;
     GemmOut o = to_buf(h->logits, h->m.vocab);
@@ -569,6 +729,7 @@ extern "C" int hy_step(hy_handle h, int32_t n_entries, const int32_t* tokens, co
   b.ent_slot = b.ent_pos0 + E; b.pages = b.ent_slot + E;
   b.T = T; b.E = E; b.max_pages = rt.max_pages_per_seq; b.page_size = rt.page_size;
   const int* want_d = b.pages + (size_t)E * rt.max_pages_per_seq;
+  h->step_start = ent_start; h->step_pos0 = ent_pos0; h->units_n = 0;
   HY_CUDA(cudaEventRecord(h->ev0, h->stream));
   if (h->m.dtype == HY_DTYPE_F32) run_step<float>(h, b, n_want, want_d, layers_out);
   else run_step<__nv_bfloat16>(h, b, n_want, want_d, layers_out);
@@ -594,5 +755,13 @@ extern "C" int hy_step(hy_handle h, int32_t n_entries, const int32_t* tokens, co
     return fail(h, HY_ERR_CUDA, "a wait inside the tensor-core matrix product ran out (pipeline stalled)");
   }
   cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1);
+  for (auto& r : h->prof_list) {
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, r.a, r.b);
+    h->prof_ms[r.cat] += ms;
+    h->ev_pool.push_back(r.a);
+    h->ev_pool.push_back(r.b);
+  }
+  h->prof_list.clear();
   return HY_OK;
 }

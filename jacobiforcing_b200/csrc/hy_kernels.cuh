@@ -161,54 +161,94 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A
   }
 }
 
-// Few-row kernel (decode steps): the weight matrix is streamed once, 16 bytes per lane per load; one warp owns one output
-// column for up to ROWS rows, the rows' operand sits in shared memory.  K order: lane-strided partial sums + xor tree.
+// Few-row kernel (decode steps): the weight matrix is streamed once, 16 bytes per lane per load, four loads in flight per
+// lane; one warp owns one output column for up to ROWS rows; the rows' operand sits in shared memory in its own type and
+// is read back 16 bytes at a time (conflict-free).  K order: lane-strided partial sums, then an xor tree.
+template <typename T, int N>
+struct VecN { T v[N]; };
+
 template <typename TA, typename TW, typename TO, int ROWS>
 __global__ void __launch_bounds__(256) gemm_rows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw,
-                                                        int T, int N, int K, GemmOut o) {
+                                                        int T, int N, int K, int ksplit, GemmOut o) {
   extern __shared__ __align__(16) unsigned char hy_smem[];
-  float* As = reinterpret_cast<float*>(hy_smem);               // [ROWS][K]
+  __shared__ float parts[8][ROWS];
+  TA* As = reinterpret_cast<TA*>(hy_smem);                     // [ROWS][Kp], Kp = K rounded up to the vector width
+  constexpr int VEC = 16 / sizeof(TW);
+  const int Kp = (K + VEC - 1) / VEC * VEC;
   const int t0 = blockIdx.y * ROWS;
-  for (int i = threadIdx.x; i < ROWS * K; i += blockDim.x) {
-    const int r = i / K, k = i % K;
-    As[i] = (t0 + r < T) ? to_f(A[(size_t)(t0 + r) * lda + k]) : 0.0f;
+  constexpr int VA = 16 / sizeof(TA);
+  if (K % VA == 0 && lda % VA == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && Kp == K) {
+    const int kv = K / VA;                                     // 16 bytes per thread per load
+    for (int i = threadIdx.x; i < ROWS * kv; i += blockDim.x) {
+      const int r = i / kv, k = (i % kv) * VA;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (t0 + r < T) v = *reinterpret_cast<const uint4*>(A + (size_t)(t0 + r) * lda + k);
+      *reinterpret_cast<uint4*>(As + r * Kp + k) = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < ROWS * Kp; i += blockDim.x) {
+      const int r = i / Kp, k = i % Kp;
+      As[i] = (t0 + r < T && k < K) ? A[(size_t)(t0 + r) * lda + k] : from_f<TA>(0.0f);
+    }
   }
   __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  constexpr int VEC = 16 / sizeof(TW);
-  for (int n = blockIdx.x * nw + warp; n < N; n += gridDim.x * nw) {
-    const TW* wr = W + (size_t)n * ldw;
+  // ksplit warps share a column (long k, few columns: more loads in flight); their sums are added in part order
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int cpb = 8 / ksplit, part = warp % ksplit, cib = warp / ksplit;
+  const int Kc = ((K + ksplit - 1) / ksplit + 32 * VEC - 1) / (32 * VEC) * (32 * VEC);
+  const int lo = part * Kc, hi = min(K, lo + Kc);
+  for (int base = blockIdx.x * cpb; base < N; base += gridDim.x * cpb) {
+    const int n = base + cib;
     float acc[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) acc[r] = 0.0f;
-    const bool vec_ok = ((reinterpret_cast<uintptr_t>(wr) & 15) == 0);
-    int kdone = 0;
-    if (vec_ok) {
-      const int kv = K / VEC * VEC;
-      for (int k = lane * VEC; k < kv; k += 32 * VEC) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(wr + k);
-        const TW* wv = reinterpret_cast<const TW*>(&raw);
+    if (n < N) {
+      const TW* wr = W + (size_t)n * ldw;
+      const bool vec_ok = ((reinterpret_cast<uintptr_t>(wr) & 15) == 0);
+      int kdone = lo;
+      if (vec_ok) {
+        const int kv = min(hi, K / VEC * VEC);
+#pragma unroll 4
+        for (int k = lo + lane * VEC; k < kv; k += 32 * VEC) {
+          const VecN<TW, VEC> wv = *reinterpret_cast<const VecN<TW, VEC>*>(wr + k);
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-          const float w = to_f(wv[j]);
+          for (int r = 0; r < ROWS; ++r) {
+            const VecN<TA, VEC> av = *reinterpret_cast<const VecN<TA, VEC>*>(As + r * Kp + k);
 #pragma unroll
-          for (int r = 0; r < ROWS; ++r) acc[r] = fmaf(As[r * K + k + j], w, acc[r]);
+            for (int j = 0; j < VEC; ++j) acc[r] = fmaf(to_f(av.v[j]), to_f(wv.v[j]), acc[r]);
+          }
+        }
+        kdone = max(lo, kv);
+      }
+      for (int k = kdone + lane; k < hi; k += 32) {
+        const float w = to_f(wr[k]);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) acc[r] = fmaf(to_f(As[r * Kp + k]), w, acc[r]);
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
+    }
+    if (ksplit > 1) {
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) parts[warp][r] = acc[r];
+      }
+      __syncthreads();
+      if (lane == 0 && part == 0) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          float v = 0.0f;
+          for (int p = 0; p < ksplit; ++p) v += parts[warp + p][r];
+          acc[r] = v;
         }
       }
-      kdone = kv;
     }
-    for (int k = kdone + lane; k < K; k += 32) {
-      const float w = to_f(wr[k]);
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) acc[r] = fmaf(As[r * K + k], w, acc[r]);
-    }
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
-    if (lane == 0) {
+    if (lane == 0 && part == 0 && n < N) {
 #pragma unroll
       for (int r = 0; r < ROWS; ++r)
         if (t0 + r < T) gemm_store<TO>(o, t0 + r, n, acc[r]);
     }
+    if (ksplit > 1) __syncthreads();
   }
 }
 
@@ -341,15 +381,26 @@ __global__ void __launch_bounds__(128) attn_sink_kernel(Batch b, const AT* __res
 // S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n ; y_c = sum_n S[c, n] C_n + D_c x_c ; out = y silu(z) out_scale.
 // L lanes (a power of two) share a channel, each holding NPER states.  dt_raw is the step-size projection before bias
 // and softplus.  low [T, ldl] holds [dt-rank part | B | C].  state [slot][inner][nstate] fp32.
+// Inputs of HY_SCAN_TB tokens are staged in shared memory by the whole block (one exposed load latency per batch of
+// tokens instead of one per token); the recurrence itself then runs out of shared memory and registers.
+constexpr int HY_SCAN_TB = 16;
 template <typename AT, typename WT, int NPER>
 __global__ void __launch_bounds__(128) scan_kernel(Batch b, const AT* __restrict__ x, int ldx, const AT* __restrict__ z, int ldz,
                                                    const float* __restrict__ dt_raw, int lddt, const WT* __restrict__ dt_bias,
                                                    const float* __restrict__ low, int ldl, int col_b, int col_c,
                                                    const float* __restrict__ A, const WT* __restrict__ D, int inner, int nstate,
                                                    int L, float out_scale, float* __restrict__ state, AT* __restrict__ out, int ldo) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
   const int e = blockIdx.y;
   const int per_block = blockDim.x / L;
-  const int c = blockIdx.x * per_block + threadIdx.x / L;
+  float* sB = reinterpret_cast<float*>(hy_smem);              // [TB][nstate]
+  float* sC = sB + HY_SCAN_TB * nstate;                       // [TB][nstate]
+  float* sdt = sC + HY_SCAN_TB * nstate;                      // [TB][per_block]
+  float* sx = sdt + HY_SCAN_TB * per_block;
+  float* sz = sx + HY_SCAN_TB * per_block;
+  const int c0 = blockIdx.x * per_block;
+  const int cl = threadIdx.x / L;
+  const int c = c0 + cl;
   const int sub = threadIdx.x % L;
   const bool live = c < inner;
   const int cc = live ? c : inner - 1;
@@ -362,26 +413,42 @@ __global__ void __launch_bounds__(128) scan_kernel(Batch b, const AT* __restrict
     S[i] = (n < nstate && pos0 > 0) ? st[n] : 0.0f;
     a[i] = n < nstate ? A[(size_t)cc * nstate + n] : 0.0f;
   }
-  const float bias = to_f(dt_bias[cc]), dd = to_f(D[cc]);
-  for (int j = 0; j < cnt; ++j) {
-    const int t = start + j;
-    const float dt = softplus_f(dt_raw[(size_t)t * lddt + cc] + bias);
-    const float xv = to_f(x[(size_t)t * ldx + cc]);
-    const float dx = dt * xv;
-    float y = 0.0f;
-#pragma unroll
-    for (int i = 0; i < NPER; ++i) {
-      const int n = sub + i * L;
-      if (n < nstate) {
-        const float bn = low[(size_t)t * ldl + col_b + n], cn = low[(size_t)t * ldl + col_c + n];
-        S[i] = fmaf(expf(dt * a[i]), S[i], dx * bn);
-        y = fmaf(S[i], cn, y);
-      }
+  const float dd = to_f(D[cc]);
+  for (int j0 = 0; j0 < cnt; j0 += HY_SCAN_TB) {
+    const int nb = min(HY_SCAN_TB, cnt - j0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb * nstate; i += blockDim.x) {
+      const int tt = i / nstate, n = i % nstate;
+      const size_t row = (size_t)(start + j0 + tt) * ldl;
+      sB[tt * nstate + n] = low[row + col_b + n];
+      sC[tt * nstate + n] = low[row + col_c + n];
     }
-    for (int o = L >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-    if (live && sub == 0) {
-      y = fmaf(dd, xv, y);
-      out[(size_t)t * ldo + c] = from_f<AT>(y * silu_f(to_f(z[(size_t)t * ldz + c])) * out_scale);
+    for (int i = threadIdx.x; i < nb * per_block; i += blockDim.x) {
+      const int tt = i / per_block, k = i % per_block;
+      const int ch = min(c0 + k, inner - 1);
+      const size_t t = (size_t)(start + j0 + tt);
+      sdt[i] = softplus_f(dt_raw[t * lddt + ch] + to_f(dt_bias[ch]));
+      sx[i] = to_f(x[t * ldx + ch]);
+      sz[i] = to_f(z[t * ldz + ch]);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nb; ++tt) {
+      const float dt = sdt[tt * per_block + cl], xv = sx[tt * per_block + cl];
+      const float dx = dt * xv;
+      float y = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NPER; ++i) {
+        const int n = sub + i * L;
+        if (n < nstate) {
+          S[i] = fmaf(expf(dt * a[i]), S[i], dx * sB[tt * nstate + n]);
+          y = fmaf(S[i], sC[tt * nstate + n], y);
+        }
+      }
+      for (int o = L >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (live && sub == 0) {
+        y = fmaf(dd, xv, y);
+        out[(size_t)(start + j0 + tt) * ldo + c] = from_f<AT>(y * silu_f(sz[tt * per_block + cl]) * out_scale);
+      }
     }
   }
   if (live) {
@@ -458,6 +525,138 @@ __global__ void delta_kernel(Batch b, const AT* __restrict__ qkv, int ldq, int c
   }
   __syncthreads();
   for (int i = tid; i < dim * vdim; i += blockDim.x) st[i] = S[i];
+}
+
+// Sum of two values over the block in one pass (same order rules as block_sum).  red: >= 66 floats.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  a = warp_sum(a); b = warp_sum(b);
+  __syncthreads();
+  if (lane == 0) { red[w] = a; red[33 + w] = b; }
+  __syncthreads();
+  if (w == 0) {
+    float sa = lane < nw ? red[lane] : 0.0f, sb = lane < nw ? red[33 + lane] : 0.0f;
+    sa = warp_sum(sa); sb = warp_sum(sb);
+    if (lane == 0) { red[32] = sa; red[65] = sb; }
+  }
+  __syncthreads();
+  return make_float2(red[32], red[65]);
+}
+
+// The same recurrence with thread j keeping column j of S in registers (key size <= DR): no shared-memory traffic for
+// the state, four partial sums per dot product so the per-token chain is short.  Same results up to summation order.
+// Inputs of HY_DELTA_TB tokens are staged by the whole block; unit vectors and decays of those tokens are made by one
+// warp per token (shuffles only), the per-token recurrence then runs without any block barrier, and the output norms of
+// the batch are again made by one warp per token: four barriers per batch of tokens instead of seven per token.
+constexpr int HY_DELTA_TB = 16;
+
+// PARTS neighbouring lanes share a column of S, each keeping DR / PARTS of its rows in registers (PARTS > 1 ends each dot
+// product in log2(PARTS) shuffles).  Measured at key size 128, 128 value columns: PARTS = 1 (one warp per scheduler, 128
+// rows in registers) 2.1 us per token, PARTS = 4 (four warps per scheduler) 3.6 us: the chain through shuffles and the
+// read-out store costs more than the shorter loops save, so the dispatcher uses PARTS = 1.
+template <typename AT, typename WT, int DR, int PARTS>
+__global__ void __launch_bounds__(DR / PARTS > 32 ? 256 : 512)
+delta_reg_kernel(Batch b, const AT* __restrict__ qkv, int ldq, int col_q, int col_k, int col_v,
+                 const AT* __restrict__ beta_in, int ldb, int col_beta, const float* __restrict__ a_in, int lda,
+                 const float* __restrict__ gate_in, int ldg, const WT* __restrict__ A_log, const WT* __restrict__ dt_bias,
+                 const WT* __restrict__ norm_w, int H, int G, int dim, int vdim, float eps, float* __restrict__ state,
+                 AT* __restrict__ out, int ldo) {
+  constexpr int RP = DR / PARTS;
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  const int nt = blockDim.x, nwarps = nt >> 5, nc = nt / PARTS;
+  float* sq = reinterpret_cast<float*>(hy_smem);               // [TB][DR] unit queries (times dim^-1/2)
+  float* skk = sq + HY_DELTA_TB * DR;                           // [TB][DR] unit keys
+  float* sa = skk + HY_DELTA_TB * DR;                           // [TB][DR] decays
+  float* sv = sa + HY_DELTA_TB * DR;                            // [TB][nc] values
+  float* sg = sv + HY_DELTA_TB * nc;                            // [TB][nc] output gates (pre-sigmoid)
+  float* so = sg + HY_DELTA_TB * nc;                            // [TB][nc] raw read-outs
+  float* sbeta = so + HY_DELTA_TB * nc;                         // [TB]
+  const int h = blockIdx.x, e = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int jc = tid / PARTS, r0 = (tid % PARTS) * RP;
+  const int g = h / (H / G);
+  const int start = b.ent_start[e], cnt = b.ent_start[e + 1] - start, pos0 = b.ent_pos0[e];
+  float* st = state + ((size_t)b.ent_slot[e] * H + h) * dim * vdim;
+  const bool col = jc < vdim;
+  float S[RP];
+#pragma unroll
+  for (int i = 0; i < RP; ++i) S[i] = (col && r0 + i < dim && pos0 > 0) ? st[(size_t)(r0 + i) * vdim + jc] : 0.0f;
+  const float rate = expf(to_f(A_log[h]));
+  const float qscale = rsqrtf((float)dim);
+  for (int j0 = 0; j0 < cnt; j0 += HY_DELTA_TB) {
+    const int nb = min(HY_DELTA_TB, cnt - j0);
+    __syncthreads();                                           // the previous batch is finished with the staging area
+    for (int i = tid; i < nb * DR; i += nt) {
+      const int tt = i / DR, k = i % DR;
+      const size_t t = (size_t)(start + j0 + tt);
+      const bool ok = k < dim;
+      sq[i] = ok ? to_f(qkv[t * ldq + col_q + g * dim + k]) : 0.0f;
+      skk[i] = ok ? to_f(qkv[t * ldq + col_k + g * dim + k]) : 0.0f;
+      sa[i] = ok ? expf(-rate * softplus_f(a_in[t * lda + h * dim + k] + to_f(dt_bias[h * dim + k]))) : 1.0f;
+    }
+    for (int i = tid; i < nb * nc; i += nt) {
+      const int tt = i / nc, k = i % nc;
+      const size_t t = (size_t)(start + j0 + tt);
+      sv[i] = k < vdim ? to_f(qkv[t * ldq + col_v + h * vdim + k]) : 0.0f;
+      sg[i] = k < vdim ? gate_in[t * ldg + h * vdim + k] : 0.0f;
+    }
+    if (tid < nb) sbeta[tid] = sigmoid_f(to_f(beta_in[(size_t)(start + j0 + tid) * ldb + col_beta + h]));
+    __syncthreads();
+    for (int tt = warp; tt < nb; tt += nwarps) {               // unit vectors: one warp per token
+      float q2 = 0.0f, k2 = 0.0f;
+      for (int k = lane; k < DR; k += 32) { q2 = fmaf(sq[tt * DR + k], sq[tt * DR + k], q2); k2 = fmaf(skk[tt * DR + k], skk[tt * DR + k], k2); }
+      q2 = warp_sum(q2); k2 = warp_sum(k2);
+      const float qi = qscale / sqrtf(q2 + 1e-6f), ki = 1.0f / sqrtf(k2 + 1e-6f);
+      for (int k = lane; k < DR; k += 32) { sq[tt * DR + k] *= qi; skk[tt * DR + k] *= ki; }
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nb; ++tt) {
+      const float* gs = sa + tt * DR + r0;
+      const float* ks = skk + tt * DR + r0;
+      const float* qs = sq + tt * DR + r0;
+      float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < RP; i += 4) {
+        const float4 g4 = *reinterpret_cast<const float4*>(&gs[i]);
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[i]);
+        S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
+        p0 = fmaf(S[i], k4.x, p0); p1 = fmaf(S[i + 1], k4.y, p1);
+        p2 = fmaf(S[i + 2], k4.z, p2); p3 = fmaf(S[i + 3], k4.w, p3);
+      }
+      float sk = (p0 + p1) + (p2 + p3);
+#pragma unroll
+      for (int o = 1; o < PARTS; o <<= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
+      const float u = sbeta[tt] * (sv[tt * nc + jc] - sk);
+      p0 = p1 = p2 = p3 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < RP; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[i]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[i]);
+        S[i] = fmaf(k4.x, u, S[i]); S[i + 1] = fmaf(k4.y, u, S[i + 1]);
+        S[i + 2] = fmaf(k4.z, u, S[i + 2]); S[i + 3] = fmaf(k4.w, u, S[i + 3]);
+        p0 = fmaf(S[i], q4.x, p0); p1 = fmaf(S[i + 1], q4.y, p1);
+        p2 = fmaf(S[i + 2], q4.z, p2); p3 = fmaf(S[i + 3], q4.w, p3);
+      }
+      float ov = (p0 + p1) + (p2 + p3);
+#pragma unroll
+      for (int o = 1; o < PARTS; o <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
+      if (tid % PARTS == 0) so[tt * nc + jc] = ov;
+    }
+    __syncthreads();
+    for (int tt = warp; tt < nb; tt += nwarps) {               // output norm and gate: one warp per token
+      float o2 = 0.0f;
+      for (int k = lane; k < vdim; k += 32) o2 = fmaf(so[tt * nc + k], so[tt * nc + k], o2);
+      o2 = warp_sum(o2);
+      const float inv = 1.0f / sqrtf(o2 / (float)vdim + eps);
+      for (int k = lane; k < vdim; k += 32)
+        out[(size_t)(start + j0 + tt) * ldo + h * vdim + k] =
+            from_f<AT>(so[tt * nc + k] * inv * to_f(norm_w[k]) * sigmoid_f(sg[tt * nc + k]));
+    }
+  }
+  if (col) {
+#pragma unroll
+    for (int i = 0; i < RP; ++i)
+      if (r0 + i < dim) st[(size_t)(r0 + i) * vdim + jc] = S[i];
+  }
 }
 
 // ---- sampling: argmax, or Gumbel-max at a temperature with a counter-based generator ---------------------------------------------

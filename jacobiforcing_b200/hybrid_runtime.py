@@ -135,6 +135,14 @@ class HybridRuntime:
         self.stats["device_ms"] += float(self.lib.hy_last_step_ms(self.h))
         return {"logits": logits, "sampled": sampled, "layers": layers}
 
+    def profile(self, on: bool) -> None:
+        cabi.check(self.lib.hy_profile_enable(self.h, 1 if on else 0), self.h)
+
+    def profile_read(self) -> Dict[str, float]:
+        ms = (C.c_float * len(cabi.PROFILE_CATEGORIES))()
+        cabi.check(self.lib.hy_profile_read(self.h, ms), self.h)
+        return dict(zip(cabi.PROFILE_CATEGORIES, (float(x) for x in ms)))
+
     @property
     def launches(self) -> int:
         return int(self.lib.hy_launch_count(self.h))

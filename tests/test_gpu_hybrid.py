@@ -165,6 +165,74 @@ def test_marked_key_far_back_is_found(needle_at, decode):
     assert rel_err(got, want) < TOL["float32"]
 
 
+def _needle_model_wide(dim, heads, kv_heads):
+    """The marked-key model at key sizes the tensor-core attention serves (bf16 build)."""
+    layer = attn_scan(heads=heads, kv_heads=kv_heads, dim=dim, conv=2, coef=0.0, every=1, scale=12.0 / (dim * 7.84), left_scale=1.0,
+                      right_scale=0.0)       # a matching key scores about 12
+    layer["mlp"] = None
+    cfg = model_config([layer], width=64, vocab=64, emb_scale=40.0)      # the token outweighs the position
+    w = plain.random_weights(cfg, 33)
+    g = torch.Generator().manual_seed(34)
+    p = torch.randn(dim, 64, generator=g) * 0.35
+    w["l0.mix.left.q"] = torch.cat([p] * heads).to(torch.bfloat16)
+    w["l0.mix.left.k"] = torch.cat([p] * kv_heads).to(torch.bfloat16)
+    for n, rows in (("q", heads * dim), ("k", kv_heads * dim)):
+        c = torch.zeros(rows, 2)
+        c[:, 1] = 1.0
+        if n == "k":
+            c[:, 0], c[:, 1] = 1.0, 0.0   # a key (= value) is the token BEFORE it: the last query matches the key right
+                                          # after the marked token and not its own
+        w[f"l0.mix.left.{n}.conv"] = c.to(torch.bfloat16)
+    w["l0.norm1"] = torch.zeros(64).to(torch.bfloat16)
+    w["l0.mix.left.o"] = (w["l0.mix.left.o"].float() * 30.0).to(torch.bfloat16)   # as large as the embedding in the stream
+    w["l0.mix.left.sink"] = torch.full((heads,), -2.0).to(torch.bfloat16)
+    return cfg, w
+
+
+@pytest.mark.parametrize("dim,heads,kv_heads", [(64, 4, 2), (32, 8, 1), (128, 2, 2)])
+@pytest.mark.parametrize("needle_at", [0, 62, 63, 254, 255, 299])      # marked keys at 1, 63, 64, 255, 256, 300
+@pytest.mark.parametrize("decode", [False, True])
+def test_marked_key_tensor_core_attention(dim, heads, kv_heads, needle_at, decode):
+    cfg, w = _needle_model_wide(dim, heads, kv_heads)
+    n = 330
+    toks = [2 + (i % 50) for i in range(n)]
+    toks[needle_at] = 60
+    toks[-1] = 60
+    want = oracle_logits(cfg, w, toks)
+    without = list(toks)
+    without[needle_at] = 2 + (needle_at % 50)
+    assert rel_err(oracle_logits(cfg, w, without)[-1], want[-1]) > 0.3
+    hz = Harness(cfg, w, "bfloat16", page_size=16, num_pages=24, slots=1)
+    try:
+        got = hz.feed("n", toks, cuts=([n - 40, 1] if decode else [100, 230]))
+    finally:
+        hz.close()
+    assert rel_err(got[-1], want[-1]) < 2e-2
+    assert rel_err(got, want) < 3e-2
+
+
+@pytest.mark.parametrize("dim,heads,kv_heads", [(64, 4, 2), (32, 16, 2), (128, 4, 1)])
+def test_tensor_core_attention_in_a_model(dim, heads, kv_heads):
+    cfg = model_config([attn_scan(heads=heads, kv_heads=kv_heads, dim=dim, every=50), delta(),
+                        attn_scan(heads=heads, kv_heads=kv_heads, dim=dim, every=64)], width=64)
+    w = plain.random_weights(cfg, 90)
+    V = cfg["vocab"]
+    reqs = {"a": rand_tokens(300, V, 91), "b": rand_tokens(70, V, 92), "c": rand_tokens(3, V, 93)}
+    ref = {k: oracle_logits(cfg, w, v) for k, v in reqs.items()}
+    hz = Harness(cfg, w, "bfloat16", page_size=16, num_pages=30, slots=3)
+    try:
+        o1 = hz.step([("a", reqs["a"][:259], range(259)), ("b", reqs["b"][:5], range(5))])
+        o2 = hz.step([("a", reqs["a"][259:260], [0]), ("b", reqs["b"][5:70], range(65)), ("c", reqs["c"], range(3))])
+        o3 = hz.step([("a", reqs["a"][260:], range(40))])
+    finally:
+        hz.close()
+    a = np.concatenate([o1[:259], o2[:1], o3], 0)
+    bb = np.concatenate([o1[259:], o2[1:66]], 0)
+    assert rel_err(a, ref["a"]) < TOL["bfloat16"]
+    assert rel_err(bb, ref["b"]) < TOL["bfloat16"]
+    assert rel_err(o2[66:], ref["c"]) < TOL["bfloat16"]
+
+
 @pytest.mark.parametrize("sink", [-20.0, 0.0, 8.0])
 def test_sink_takes_its_share(sink):
     cfg, w = _needle_model()
