@@ -452,7 +452,8 @@ int gemm(hy_engine* h, const TA* A, int lda, const TW* Wt, int ldw, int T, int N
         cudaFuncSetAttribute(gemm_tc_kernel<TO, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(256));
         attr_set = true;
       }
-      if (T > 128)
+      // 256-row tiles halve the weight traffic per row; 128-row tiles when the wider ones would leave SMs without a CTA
+      if (T > 128 && (long long)((N + 127) / 128) * ((T + 255) / 256) >= 148)
         gemm_tc_kernel<TO, 256><<<dim3((N + 127) / 128, (T + 255) / 256), 192, tc_smem_bytes(256), h->stream>>>(
             A, lda, (const bf16*)tiled, T, N, K, o, h->err_d);
       else
@@ -471,9 +472,16 @@ int gemm(hy_engine* h, const TA* A, int lda, const TW* Wt, int ldw, int T, int N
     const int cpb = 8 / ksplit;
     const int blocks = std::min((N + cpb - 1) / cpb, 148 * 16);
     const int fit = (int)((200 * 1024) / row_bytes);
+    static bool rows_attr = false;                        // per <TA, TW, TO>: this function is a template
+    if (!rows_attr) {
+      cudaFuncSetAttribute(gemm_rows_kernel<TA, TW, TO, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      cudaFuncSetAttribute(gemm_rows_kernel<TA, TW, TO, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      cudaFuncSetAttribute(gemm_rows_kernel<TA, TW, TO, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      cudaFuncSetAttribute(gemm_rows_kernel<TA, TW, TO, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      rows_attr = true;
+    }
     auto launch = [&](auto kern, int rows) {
       const size_t smem = (size_t)rows * row_bytes;
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
       kern<<<dim3(blocks, (T + rows - 1) / rows), 256, smem, h->stream>>>(A, lda, Wt, ldw, T, N, K, ksplit, o);
     };
     if (T == 1 || fit < 2) launch(gemm_rows_kernel<TA, TW, TO, 1>, 1);
@@ -649,7 +657,8 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
         delta_reg_kernel<AT, float, 128, 1><<<dim3(c.d_heads, E), nthr, dsm(128, nthr), s>>>(HY_DELTA_ARGS);
       else {
         const size_t smem = ((size_t)c.d_dim * c.d_vdim + 3 * c.d_dim + 40) * 4;
-        cudaFuncSetAttribute(delta_kernel<AT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        static bool dk_attr = false;
+        if (!dk_attr) { cudaFuncSetAttribute(delta_kernel<AT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); dk_attr = true; }
         delta_kernel<AT, float><<<dim3(c.d_heads, E), threads, smem, s>>>(HY_DELTA_ARGS);
       }
 #undef HY_DELTA_ARGS

@@ -62,14 +62,23 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const bf16* __restrict__ X
     // ---- activation producers ------------------------------------------------------------------------------------
     for (int kt = 0; kt < KT; ++kt) {
       const int s = kt % TC_STAGES;
-      if (!tc_wait(&sm->empty[s], ((kt / TC_STAGES) & 1) ^ 1, sm, err)) break;
       unsigned char* xt = base + s * SLOT + TC_WTILE;
-      for (int i = threadIdx.x; i < BT * 8; i += 128) {
+      // all loads of the stage first (BT / 16 independent 16-byte loads per thread in flight), then the swizzled stores
+      uint4 v[BT / 16];
+#pragma unroll
+      for (int u = 0; u < BT / 16; ++u) {
+        const int i = threadIdx.x + u * 128;
         const int r = i >> 3, c = i & 7;
         const int t = t0 + r, k = kt * 64 + c * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (t < T && k < K) v = *reinterpret_cast<const uint4*>(X + (size_t)t * lda + k);
-        *reinterpret_cast<uint4*>(xt + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+        v[u] = make_uint4(0, 0, 0, 0);
+        if (t < T && k < K) v[u] = *reinterpret_cast<const uint4*>(X + (size_t)t * lda + k);
+      }
+      if (!tc_wait(&sm->empty[s], ((kt / TC_STAGES) & 1) ^ 1, sm, err)) break;     // the slot is free: MMAs that read it retired
+#pragma unroll
+      for (int u = 0; u < BT / 16; ++u) {
+        const int i = threadIdx.x + u * 128;
+        const int r = i >> 3, c = i & 7;
+        *reinterpret_cast<uint4*>(xt + r * 128 + ((c ^ (r & 7)) << 4)) = v[u];
       }
       jf::fence_proxy_async_smem();
       jf::mbar_arrive(&sm->full[s]);

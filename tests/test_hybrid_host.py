@@ -148,3 +148,27 @@ def test_oracle_mechanisms_agree_with_direct_formulas():
     h = torch.tensor([[1.0, 2.0]], dtype=torch.float64)
     share = np.exp(5.0) / (np.exp(5.0) + np.exp(0.5))
     assert np.allclose(plain.sink_attention(h, p, c).numpy(), [[0.5 * share * 1.0, 0.5 * share * 2.0]])
+
+
+def test_header_symbols_match_the_binding():
+    import re
+    from jacobiforcing_b200 import _hybrid_cabi
+    src = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "jacobi_hybrid.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    declared = sorted(set(re.findall(r"\b(hy_[a-z_0-9]+)\s*\(", src)))
+    assert declared == sorted(_hybrid_cabi.EXPORTS)
+    import ctypes
+    lib = ctypes.CDLL(_hybrid_cabi.build())
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared but not exported"
+
+
+def test_no_cpu_fallback_for_the_hybrid_engine():
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    from jacobiforcing_b200.hybrid_config import HybridConfig
+    from jacobiforcing_b200.hybrid_runtime import HybridRuntime
+    w = plain.random_weights(SMALL, 0)
+    hc = HybridConfig.from_dict(SMALL, {k: tuple(v.shape) for k, v in w.items()})
+    with pytest.raises(RuntimeError, match="no CUDA device"):
+        HybridRuntime(hc)
