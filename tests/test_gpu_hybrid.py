@@ -325,6 +325,51 @@ def test_greedy_generation_through_llm_generate():
             seq.append(tok)
 
 
+def test_generate_command_line_and_trace_replay_on_a_checkpoint_directory(tmp_path):
+    """A checkpoint directory (config.json + model.safetensors) through the registry: the generate command line gives the
+    oracle's greedy tokens, and bin/trace_run writes the oracle's logits for a replayed trace."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from tests.test_hybrid_host import _write_checkpoint
+    w = plain.random_weights(SMALL, 75, low=6)
+    _write_checkpoint(tmp_path, SMALL, w)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prompt = rand_tokens(21, SMALL["vocab"], 76)
+    out = subprocess.run([sys.executable, "-m", "jacobiforcing_b200.generate", "--model", str(tmp_path), "--prompt-ids",
+                          ",".join(map(str, prompt)), "--max-tokens", "6", "--dtype", "float32", "--page-size", "16",
+                          "--max-model-len", "64", "--max-num-batched-tokens", "64"], cwd=root, capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr[-2000:]
+    ids = json.loads(out.stdout.strip().splitlines()[-1])["token_ids"]
+    seq = list(prompt)
+    for tok in ids:
+        lg = oracle_logits(SMALL, w, seq)[-1]
+        assert tok == int(np.argmax(lg)) or lg.max() - lg[tok] < 1e-3 * (lg.max() - lg.min())
+        seq.append(tok)
+    # trace replay: two requests, portions beside single tokens, one ends and its slot is used again
+    a, b = rand_tokens(30, SMALL["vocab"], 77), rand_tokens(9, SMALL["vocab"], 78)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:17], "want": [0, 16]}, {"id": "b", "tokens": b[:2], "want": [1]}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[2:], "want": [6]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[17:18], "want": [0]}, {"id": "c", "tokens": b, "want": [8]}], "end": ["c"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[18:], "want": []}], "end": ["a"]}]
+    outdir = tmp_path / "out"
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out",
+                        str(outdir), "--max-tokens", "128", "--page-size", "16"], input="\n".join(json.dumps(x) for x in steps) + "\n",
+                       cwd=root, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [ln for ln in r.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    la, lb = oracle_logits(SMALL, w, a), oracle_logits(SMALL, w, b)
+    V = SMALL["vocab"]
+    g0 = np.fromfile(outdir / "0.f32", dtype="<f4").reshape(-1, V)
+    g1 = np.fromfile(outdir / "1.f32", dtype="<f4").reshape(-1, V)
+    g2 = np.fromfile(outdir / "2.f32", dtype="<f4").reshape(-1, V)
+    assert not (outdir / "3.f32").exists()
+    assert rel_err(g0, np.stack([la[0], la[16], lb[1]])) < TOL["float32"]
+    assert rel_err(g1, lb[8:9]) < TOL["float32"]
+    assert rel_err(g2, np.stack([la[17], lb[8]])) < TOL["float32"]
+
+
 def test_sampling_at_a_temperature_follows_the_distribution():
     from tests.hybrid_helpers import Harness as H
     cfg = model_config([delta(ff=0)], width=32, vocab=12)
