@@ -56,7 +56,7 @@ struct hy_engine {
   std::vector<hy_layer_cfg> lc;
   std::map<std::string, HostTensor> host;
   std::vector<LayerW> lw;
-  void* embed = nullptr; void* final_norm = nullptr; void* head = nullptr; void* head_t = nullptr; float* inv_freq = nullptr;
+  void* embed = nullptr; void* final_norm = nullptr; void* head = nullptr; void* head_t = nullptr; double* inv_freq = nullptr;
   int* err_d = nullptr; int* err_h = nullptr;
   // per-category device times (hy_profile_enable): event pairs recorded around groups of launches
   bool prof_on = false;
@@ -289,9 +289,12 @@ extern "C" int hy_finalize(hy_handle h) {
   if (auto t = B.get("final.norm", W, -1)) h->final_norm = B.up(t->v);
   if (auto t = B.get("head", V, W)) { h->head = B.up(t->v); h->head_t = B.up_tiled(t->v, V, W); }
   {
-    std::vector<float> f((W + 1) / 2);
-    for (size_t i = 0; i < f.size(); ++i) f[i] = (float)pow(10000.0, -2.0 * (double)i / (double)W);
-    h->inv_freq = B.up_f32(f);
+    std::vector<double> f((W + 1) / 2);
+    for (size_t i = 0; i < f.size(); ++i) f[i] = pow(10000.0, -2.0 * (double)i / (double)W);
+    void* d = nullptr;
+    if (dev_alloc(h, &d, f.size() * 8, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
+    cudaMemcpy(d, f.data(), f.size() * 8, cudaMemcpyHostToDevice);
+    h->inv_freq = (double*)d;
   }
   h->lw.resize(h->lc.size());
   int max_in = 1, max_out = 1, max_cv = 1, max_f1 = 1, max_f2 = 1;

@@ -65,16 +65,17 @@ struct Batch {
 };
 
 // ---- embedding: table row times a scale, plus the sinusoid of the position ----------------------------------------------
-// entry 2i = sin(p f_i), entry 2i+1 = cos(p f_i); f_i comes from a host-made fp32 table (10000^(-2i / width)).
+// entry 2i = sin(p f_i), entry 2i+1 = cos(p f_i); f_i = 10000^(-2i / width) comes from a host-made fp64 table and the angle
+// is formed and reduced in fp64 (at position 1000 an fp32 angle is already 6e-5 off), the result enters the fp32 stream.
 template <typename WT>
-__global__ void embed_kernel(Batch b, const WT* __restrict__ table, const float* __restrict__ inv_freq, float scale,
+__global__ void embed_kernel(Batch b, const WT* __restrict__ table, const double* __restrict__ inv_freq, float scale,
                              int width, float* __restrict__ x) {
   const int t = blockIdx.x;
   const int tok = b.tok[t];
-  const float p = (float)b.tok_pos[t];
+  const double p = (double)b.tok_pos[t];
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    const float ang = p * inv_freq[c >> 1];
-    const float pe = (c & 1) ? cosf(ang) : sinf(ang);
+    const double ang = p * inv_freq[c >> 1];
+    const float pe = (float)((c & 1) ? cos(ang) : sin(ang));
     x[(size_t)t * width + c] = to_f(table[(size_t)tok * width + c]) * scale + pe;
   }
 }

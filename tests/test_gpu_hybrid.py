@@ -290,6 +290,8 @@ OTHER = [
     model_config([delta(heads=6, kv_heads=2, dim=40, vdim=40, conv=5),
                   attn_scan(heads=8, kv_heads=2, dim=48, conv=5, inner=70, state=150, dt_rank=9, sconv=6, every=1)],
                  width=72, vocab=130, emb_scale=1.0, logit_scale=1.0, eps=1e-6),
+    # a delta-rule key size beyond what a thread keeps in registers (the state lives in shared memory), width not a multiple of 8
+    model_config([delta(heads=2, kv_heads=1, dim=136, vdim=24, conv=2), attn_scan(heads=2, kv_heads=1, dim=40)], width=44, vocab=61),
 ]
 
 
