@@ -1,6 +1,8 @@
-/* jacobi_hybrid.h — C ABI of libjf_hybrid.so: layered hybrid decoders (softmax attention with a sink whose values are
- * its keys, selective scans, gated delta rule layers, squared-ReLU feed-forward; one norm per layer feeding mixer and
- * feed-forward side by side) on B200.
+/* jacobi_hybrid.h — C ABI of libjf_hybrid.so: layered hybrid decoders on B200.  Two block layouts over one residual
+ * stream: one RMS norm per layer feeding mixer and feed-forward side by side (softmax attention with a sink whose values
+ * are its keys, selective scans, gated delta rule layers, squared-ReLU feed-forward), and norm - sublayer - norm blocks
+ * with element-wise tanh norms and per-channel layer scales (scalar-decay state-space recurrence, attention over a shared
+ * low-rank latent with a rotated key part, gated linear recurrence, routed gated experts).
  *
  * Same conventions as jacobi_b200.h: every function returns 0 or a negative status, hy_last_error(h) gives the text,
  * plain pointers and sizes only, host buffers are caller-owned, device memory belongs to the handle, one host thread per
@@ -24,8 +26,15 @@ typedef struct hy_engine* hy_handle;
 
 typedef enum { HY_OK = 0, HY_ERR_INVALID = -1, HY_ERR_CUDA = -2, HY_ERR_CAPACITY = -3, HY_ERR_UNSUPPORTED = -4 } hy_status;
 typedef enum { HY_DTYPE_BF16 = 0, HY_DTYPE_F32 = 1, HY_DTYPE_F16 = 2, HY_DTYPE_I32 = 3 } hy_dtype;
-typedef enum { HY_MIX_ATTN_SCAN = 0, HY_MIX_DELTA = 1 } hy_mixer_kind;
-typedef enum { HY_FF_NONE = 0, HY_FF_RELU2 = 1 } hy_ff_kind;
+typedef enum { HY_MIX_ATTN_SCAN = 0, HY_MIX_DELTA = 1, HY_MIX_SSD = 2, HY_MIX_LATENT = 3, HY_MIX_GLR = 4 } hy_mixer_kind;
+typedef enum { HY_FF_NONE = 0, HY_FF_RELU2 = 1, HY_FF_ROUTED = 2 } hy_ff_kind;
+/* norm of the residual stream: RMS with a weight stored as an offset from one | tanh(alpha x) w + b (no statistics) */
+typedef enum { HY_NORM_RMS_OFFSET = 0, HY_NORM_TANH = 1 } hy_norm_kind;
+/* HY_BLOCK_PARALLEL: x += mixer(n(x)) + ff(n(x)), one norm per layer.
+ * HY_BLOCK_SANDWICH: x += ls1 * n1b(mixer(n1(x))), then x += ls2 * n2b(ff(n2(x))): a norm on both sides of each sublayer
+ * and a per-channel layer scale. */
+typedef enum { HY_BLOCK_PARALLEL = 0, HY_BLOCK_SANDWICH = 1 } hy_block_kind;
+typedef enum { HY_POS_SINUSOID = 0, HY_POS_NONE = 1 } hy_pos_kind;   /* what is added to the scaled embedding */
 
 typedef struct {
   int32_t mixer;                   /* hy_mixer_kind */
@@ -39,13 +48,31 @@ typedef struct {
   /* HY_MIX_DELTA: value heads, query/key heads, key size, value size, conv taps, inner sizes of the two-step decay and
    * gate projections (read from the tensor shapes) */
   int32_t d_heads, d_kv_heads, d_dim, d_vdim, d_conv, d_low_a, d_low_g;
-  int32_t ff_kind, ff;             /* hy_ff_kind, hidden size of the feed-forward */
+  int32_t ff_kind, ff;             /* hy_ff_kind, hidden size of the feed-forward (of one expert when routed) */
+  /* HY_MIX_SSD (state-space recurrence with one decay per head): heads, channels per head, state size, groups that share
+   * B and C, conv taps, parts of the gated output norm */
+  int32_t m_heads, m_vdim, m_state, m_groups, m_conv, m_norm_groups;
+  /* HY_MIX_LATENT (attention over a shared low-rank latent): heads, unrotated and rotated query/key size per head,
+   * value size, ranks of the key/value and the query latent, the layer whose cached latent is used (-1: its own),
+   * the score scale; rotation over the first r_dims of the rotated part with base r_base, frequencies interpolated by
+   * r_factor between the wavelengths original / r_fast and original / r_slow (r_factor <= 0: plain rotation) */
+  int32_t l_heads, l_dim, l_rot_dim, l_vdim, l_kv_rank, l_q_rank, l_kv_from;
+  float l_scale;
+  int32_t r_dims;
+  float r_base, r_factor, r_original, r_fast, r_slow;
+  /* HY_MIX_GLR (gated linear recurrence, forget gate = 1 - input gate, bounded below per channel) */
+  int32_t g_heads, g_dim, g_vdim;
+  /* HY_FF_ROUTED: experts, experts used per token, groups of neighbouring experts, groups a token may choose from,
+   * factor on the normalised weights */
+  int32_t x_experts, x_top, x_groups, x_keep;
+  float x_scale;
 } hy_layer_cfg;
 
 typedef struct {
   int32_t width, vocab, n_layers;
   int32_t dtype;                   /* HY_DTYPE_BF16: bf16 operands, fp32 accumulation / state / residual; HY_DTYPE_F32: all fp32 */
   float emb_scale, logit_scale, norm_eps;
+  int32_t norm_kind, block_kind, pos_kind;   /* hy_norm_kind, hy_block_kind, hy_pos_kind */
 } hy_model_cfg;
 
 typedef struct {
@@ -86,7 +113,8 @@ int hy_memory_info(hy_handle h, int64_t* weights, int64_t* cache, int64_t* state
 
 /* Device time per group of kernels, summed over the steps since hy_profile_enable(h, 1): ms[HY_PROFILE_CATEGORIES]. */
 enum { HY_PROF_NORM = 0, HY_PROF_GEMM_IN = 1, HY_PROF_CONV = 2, HY_PROF_ATTN = 3, HY_PROF_SMALL_GEMM = 4, HY_PROF_SCAN = 5,
-       HY_PROF_DELTA = 6, HY_PROF_GEMM_OUT = 7, HY_PROF_HEAD = 8, HY_PROFILE_CATEGORIES = 9 };
+       HY_PROF_DELTA = 6, HY_PROF_GEMM_OUT = 7, HY_PROF_HEAD = 8, HY_PROF_ROUTE = 9, HY_PROF_EXPERTS = 10,
+       HY_PROFILE_CATEGORIES = 11 };
 int hy_profile_enable(hy_handle h, int32_t on);
 int hy_profile_read(hy_handle h, float* ms);
 

@@ -10,12 +10,14 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libjf_hybrid.so")
-SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("hy_engine.cu", "hy_kernels.cuh", "hy_gemm.cuh", "hy_attn.cuh", "jf_ptx.cuh")] + [
+SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("hy_engine.cu", "hy_kernels.cuh", "hy_gemm.cuh", "hy_attn.cuh", "hy_mixers.cuh", "hy_experts.cuh",
+                                                        "jf_ptx.cuh")] + [
     os.path.join(ROOT, "include", "jacobi_hybrid.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]
 EXPORTS = ["hy_create", "hy_destroy", "hy_last_error", "hy_load_tensor", "hy_finalize", "hy_step", "hy_launch_count",
            "hy_last_step_ms", "hy_memory_info", "hy_profile_enable", "hy_profile_read"]
-PROFILE_CATEGORIES = ("norm_embed", "gemm_in", "conv_cache", "attention", "small_gemm", "scan", "delta", "gemm_out", "head")
+PROFILE_CATEGORIES = ("norm_embed", "gemm_in", "conv_cache", "attention", "small_gemm", "scan", "delta", "gemm_out", "head",
+                      "route", "experts")
 HY_OK, HY_ERR_INVALID, HY_ERR_CUDA, HY_ERR_CAPACITY, HY_ERR_UNSUPPORTED = 0, -1, -2, -3, -4
 
 
@@ -26,12 +28,19 @@ class LayerCfg(C.Structure):
                 [(n, C.c_int32) for n in ("s_inner", "s_state", "s_dt_rank", "s_conv")] +
                 [("left_scale", C.c_float), ("right_scale", C.c_float)] +
                 [(n, C.c_int32) for n in ("d_heads", "d_kv_heads", "d_dim", "d_vdim", "d_conv", "d_low_a", "d_low_g",
-                                          "ff_kind", "ff")])
+                                          "ff_kind", "ff")] +
+                [(n, C.c_int32) for n in ("m_heads", "m_vdim", "m_state", "m_groups", "m_conv", "m_norm_groups")] +
+                [(n, C.c_int32) for n in ("l_heads", "l_dim", "l_rot_dim", "l_vdim", "l_kv_rank", "l_q_rank", "l_kv_from")] +
+                [("l_scale", C.c_float), ("r_dims", C.c_int32)] +
+                [(n, C.c_float) for n in ("r_base", "r_factor", "r_original", "r_fast", "r_slow")] +
+                [(n, C.c_int32) for n in ("g_heads", "g_dim", "g_vdim", "x_experts", "x_top", "x_groups", "x_keep")] +
+                [("x_scale", C.c_float)])
 
 
 class ModelCfg(C.Structure):
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32),
-                ("emb_scale", C.c_float), ("logit_scale", C.c_float), ("norm_eps", C.c_float)]
+                ("emb_scale", C.c_float), ("logit_scale", C.c_float), ("norm_eps", C.c_float),
+                ("norm_kind", C.c_int32), ("block_kind", C.c_int32), ("pos_kind", C.c_int32)]
 
 
 class RuntimeCfg(C.Structure):

@@ -21,7 +21,7 @@ struct AttnUnit { int entry, kv_head, row0, split; };   // row0: first row of th
 template <int DIM>
 __global__ void __launch_bounds__(128) attn_mma_kernel(Batch b, const AttnUnit* __restrict__ units, const bf16* __restrict__ q,
                                                        int ldq, const bf16* __restrict__ cache, int H, int G, float scale,
-                                                       float qt_coef, int qt_every, int split_keys, int n_splits,
+                                                       float qt_coef, int qt_every, int split_keys, int n_splits, int vdim,
                                                        float* __restrict__ part_o, float* __restrict__ part_ml) {
   constexpr int LD = DIM + 8;                           // padded row (elements): ldmatrix rows fall into distinct banks
   __shared__ __align__(16) bf16 qs[64 * LD];
@@ -148,7 +148,8 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(Batch b, const AttnUnit* 
         }
       }
 #pragma unroll
-      for (int np = 0; np < DIM / 16; ++np) {            // two dim blocks of 8 per ldmatrix
+      for (int np = 0; np < DIM / 16; ++np) {            // two dim blocks of 8 per ldmatrix; values: the first vdim dims
+        if (np * 16 >= vdim) continue;
         uint32_t b0, b1, b2, b3;
         const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         jf::ldmatrix_x4_trans(jf::smem_u32(&ks[key * LD + np * 16 + (lane >> 4) * 8]), b0, b1, b2, b3);
@@ -179,10 +180,11 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(Batch b, const AttnUnit* 
 }
 
 // Merge the key splits of one (token, head) with the sink, gate the result, scale it, write the projection's operand.
-template <typename WT>
+// part_o rows are dim wide; the first vdim of them are values.
+template <typename WT, typename OT>
 __global__ void attn_combine_kernel(Batch b, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const WT* __restrict__ sink, const bf16* __restrict__ gate, int ldg, int H, int dim,
-                                    int split_keys, int n_splits, float out_scale, bf16* __restrict__ out, int ldo) {
+                                    int vdim, int split_keys, int n_splits, float out_scale, OT* __restrict__ out, int ldo) {
   const int t = blockIdx.x / H, h = blockIdx.x % H;
   const int live = b.tok_pos[t] / split_keys + 1;          // splits that hold a key this row may see
   const float sk = to_f(sink[h]);
@@ -192,11 +194,11 @@ __global__ void attn_combine_kernel(Batch b, const float* __restrict__ part_o, c
   float L = expf(sk - M);
   for (int s = 0; s < live; ++s) L += part_ml[(slot0 + s) * 2 + 1] * expf(part_ml[(slot0 + s) * 2] - M);
   const float inv = 1.0f / L;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
     float acc = 0.0f;
     for (int s = 0; s < live; ++s) acc += part_o[(slot0 + s) * dim + d] * expf(part_ml[(slot0 + s) * 2] - M);
-    const float gt = sigmoid_f(to_f(gate[(size_t)t * ldg + h * dim + d]));
-    out[(size_t)t * ldo + h * dim + d] = from_f<bf16>(acc * inv * gt * out_scale);
+    const float gt = gate ? sigmoid_f(to_f(gate[(size_t)t * ldg + h * vdim + d])) : 1.0f;
+    out[(size_t)t * ldo + h * vdim + d] = from_f<OT>(acc * inv * gt * out_scale);
   }
 }
 

@@ -17,6 +17,8 @@
 #include "hy_kernels.cuh"
 #include "hy_gemm.cuh"
 #include "hy_attn.cuh"
+#include "hy_mixers.cuh"
+#include "hy_experts.cuh"
 
 namespace hy {
 
@@ -44,6 +46,20 @@ struct LayerW {
   // the same matrices as swizzled 128 x 64 tiles for the tensor-core product (bf16 build)
   void* w_in_t = nullptr; void* w_out_t = nullptr; void* w_x_t = nullptr; void* w_a2_t = nullptr; void* w_g2_t = nullptr;
   float* conv_state = nullptr; float* conv_state2 = nullptr; float* rec_state = nullptr;
+  // norm - sublayer - norm blocks: the four norms and two layer scales of a layer
+  TanhNorm n1{}, n1b{}, n2{}, n2b{};
+  float* ls1 = nullptr; float* ls2 = nullptr;
+  // state-space recurrence with one decay per head
+  void* m_conv_w = nullptr; void* m_conv_b = nullptr;
+  float* m_dt_bias = nullptr; float* m_A_log = nullptr; float* m_D = nullptr; float* m_norm = nullptr;
+  // attention over a shared latent
+  float* l_qn = nullptr; float* l_kn = nullptr;
+  void* w_uq = nullptr; void* w_uq_t = nullptr; void* w_uk = nullptr; void* w_uvT = nullptr;
+  Rotation rot{};
+  // gated linear recurrence
+  float* g_fb = nullptr; float* g_lower = nullptr; float* g_norm = nullptr;
+  // routed experts: router [experts, width], gate/up [experts][2 ff][width], down [experts][width][ff]
+  void* w_router = nullptr; void* w_gu = nullptr; void* w_down = nullptr;
 };
 
 }  // namespace hy
@@ -57,6 +73,11 @@ struct hy_engine {
   std::map<std::string, HostTensor> host;
   std::vector<LayerW> lw;
   void* embed = nullptr; void* final_norm = nullptr; void* head = nullptr; void* head_t = nullptr; double* inv_freq = nullptr;
+  TanhNorm final_tanh{};
+  // routed feed-forward: choices and weights per (token, choice) pair, the sorted order, the tile list
+  int* x_ids = nullptr; float* x_wts = nullptr; int* x_counts = nullptr; int* x_offs = nullptr; int* x_fill = nullptr;
+  int* x_tile_e = nullptr; int* x_tile_r0 = nullptr; int* x_meta = nullptr; int* x_row_tok = nullptr; int* x_pair_row = nullptr;
+  int x_max_tiles = 0;
   int* err_d = nullptr; int* err_h = nullptr;
   // per-category device times (hy_profile_enable): event pairs recorded around groups of launches
   bool prof_on = false;
@@ -150,10 +171,41 @@ extern "C" int hy_create(const hy_model_cfg* model, const hy_layer_cfg* layers, 
       if (c.d_dim > 1024 || c.d_vdim > 1024) return bad("delta head sizes above 1024");
       if ((size_t)c.d_dim * c.d_vdim * 4 > 200 * 1024) return bad("delta state of one head exceeds shared memory");
       if (c.d_conv > HY_MAX_TAPS || c.d_conv < 1) return bad("conv taps must lie in 1..16");
+    } else if (c.mixer == HY_MIX_SSD) {
+      if (c.m_heads <= 0 || c.m_vdim <= 0 || c.m_groups <= 0 || c.m_heads % c.m_groups) return bad("recurrence heads must be a multiple of its groups");
+      if (c.m_state > 256 || c.m_state <= 0) return bad("recurrence state size must lie in 1..256");
+      if (c.m_conv > HY_MAX_TAPS || c.m_conv < 1) return bad("conv taps must lie in 1..16");
+      if (c.m_norm_groups <= 0 || (c.m_heads * c.m_vdim) % c.m_norm_groups) return bad("the output norm's parts must divide heads * vdim");
+    } else if (c.mixer == HY_MIX_LATENT) {
+      if (c.l_heads <= 0 || c.l_dim <= 0 || c.l_vdim <= 0 || c.l_kv_rank <= 0 || c.l_q_rank <= 0 || c.l_rot_dim < 0) return bad("latent attention sizes must be positive");
+      if (c.l_kv_rank + c.l_rot_dim > 32 * HY_ATT_MAXD) return bad("latent rank + rotated size above 640");
+      if (c.r_dims < 0 || c.r_dims % 2 || c.r_dims > c.l_rot_dim) return bad("rotated dimensions must be even and at most rot_dim");
+      const int idx = (int)(&c - h->lc.data());
+      if (c.l_kv_from >= 0) {
+        if (c.l_kv_from >= idx) return bad("a borrowed latent must come from an earlier layer");
+        const hy_layer_cfg& o = h->lc[c.l_kv_from];
+        if (o.mixer != HY_MIX_LATENT || o.l_kv_from >= 0 || o.l_kv_rank != c.l_kv_rank || o.l_rot_dim != c.l_rot_dim)
+          return bad("a borrowed latent must come from a latent-attention layer with its own down-projection and equal sizes");
+      }
+    } else if (c.mixer == HY_MIX_GLR) {
+      if (c.g_heads <= 0 || c.g_dim <= 0 || c.g_vdim <= 0) return bad("gated linear recurrence sizes must be positive");
+      if (((size_t)c.g_dim * c.g_vdim + 2 * c.g_dim + c.g_vdim + 40) * 4 > 200 * 1024 && (c.g_dim > 128 || c.g_vdim > 256))
+        return bad("gated linear recurrence: the state of one head exceeds shared memory");
     } else {
       return bad("unknown mixer kind");
     }
+    const bool sandwich_mixer = c.mixer == HY_MIX_SSD || c.mixer == HY_MIX_LATENT || c.mixer == HY_MIX_GLR;
+    if (sandwich_mixer != (model->block_kind == HY_BLOCK_SANDWICH)) return bad("this mixer does not belong to the model's block layout");
+    if ((c.ff_kind == HY_FF_ROUTED) != (model->block_kind == HY_BLOCK_SANDWICH) && c.ff_kind != HY_FF_NONE)
+      return bad("this feed-forward does not belong to the model's block layout");
+    if (c.ff_kind == HY_FF_ROUTED) {
+      if (c.x_experts <= 0 || c.x_experts > 4096 || c.x_groups <= 0 || c.x_experts % c.x_groups) return bad("experts must split into equal groups");
+      if (c.x_keep < 1 || c.x_keep > c.x_groups) return bad("kept groups outside 1..groups");
+      if (c.x_top < 1 || c.x_top > c.x_keep * (c.x_experts / c.x_groups)) return bad("more experts per token than the kept groups hold");
+      if (c.ff <= 0) return bad("expert size must be positive");
+    }
   }
+  if ((model->block_kind == HY_BLOCK_SANDWICH) != (model->norm_kind == HY_NORM_TANH)) return bad("block layout and norm kind do not go together");
   if (cudaSetDevice(rt->device) != cudaSuccess) return bad("cudaSetDevice failed");
   cudaStreamCreate(&h->stream);
   cudaEventCreate(&h->ev0);
@@ -273,6 +325,161 @@ struct Builder {
   }
 };
 
+void stack_rows(std::vector<float>& dst, const HostTensor* t);
+
+// Frequencies of a rotation over `dims` dimensions: base^(-2i / dims), interpolated between two wavelengths when a
+// factor is given (pairs that turn more than `fast` times over `original` positions keep their frequency, pairs that
+// turn fewer than `slow` times are divided by the factor, a linear ramp over the pair index lies between), and the factor
+// 0.1 ln(factor) + 1 on cosine and sine.
+void rotation_table(const hy_layer_cfg& c, std::vector<double>& f, float* mag) {
+  const int dims = c.r_dims;
+  f.resize((size_t)dims / 2);
+  const double base = (double)c.r_base;
+  for (int i = 0; i < dims / 2; ++i) f[(size_t)i] = pow(base, -2.0 * (double)i / (double)dims);
+  *mag = 1.0f;
+  if (c.r_factor > 0.0f && dims > 0) {
+    const double kPi = 3.14159265358979323846;
+    auto turn_dim = [&](double turns) { return (double)dims * log((double)c.r_original / (2.0 * kPi * turns)) / (2.0 * log(base)); };
+    const double lo = std::max(floor(turn_dim((double)c.r_fast)), 0.0);
+    const double hi = std::min(ceil(turn_dim((double)c.r_slow)), (double)(dims - 1));
+    for (int i = 0; i < dims / 2; ++i) {
+      const double ramp = std::min(std::max(((double)i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+      f[(size_t)i] = f[(size_t)i] / (double)c.r_factor * ramp + f[(size_t)i] * (1.0 - ramp);
+    }
+    *mag = (float)(0.1 * log((double)c.r_factor) + 1.0);
+  }
+}
+
+struct Maxima { int in = 1, out = 1, cv = 1, f1 = 1, f2 = 1; };
+
+bool tanh_norm_load(Builder& B, const std::string& name, int W, TanhNorm* n) {
+  const HostTensor* w = B.get(name, W, -1);
+  const HostTensor* b = B.get(name + ".b", W, -1);
+  auto it = B.h->host.find(name + ".alpha");
+  if (it == B.h->host.end() || it->second.v.size() != 1) {
+    if (B.rc == HY_OK) B.rc = fail(B.h, HY_ERR_INVALID, "missing or non-scalar tensor " + name + ".alpha");
+    return false;
+  }
+  if (!w || !b) return false;
+  n->w = B.up_f32(w->v);
+  n->b = B.up_f32(b->v);
+  n->alpha = it->second.v[0];
+  return true;
+}
+
+// One layer of a norm - sublayer - norm model: its norms and layer scales, the mixer's merged input projection, the
+// mixer's small tensors, its output projection, state and cache, and the experts.
+int finalize_sandwich_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
+  const hy_layer_cfg& c = h->lc[i];
+  const hy_runtime_cfg& rt = h->rt;
+  LayerW& L = h->lw[i];
+  const int W = h->m.width;
+  const std::string p = "l" + std::to_string(i) + ".", d = p + "mix.";
+  tanh_norm_load(B, p + "norm1", W, &L.n1);
+  tanh_norm_load(B, p + "norm1b", W, &L.n1b);
+  if (auto t = B.get(p + "ls1", W, -1)) L.ls1 = B.up_f32(t->v);
+  std::vector<float> win;
+  int n_in = 0, k_out = 0;
+  if (c.mixer == HY_MIX_SSD) {
+    const int H = c.m_heads, inner = H * c.m_vdim, GN = c.m_groups * c.m_state, C = inner + 2 * GN;
+    n_in = 2 * inner + 2 * GN + H;
+    stack_rows(win, B.get(d + "in", n_in, W));
+    if (auto t = B.get(d + "conv", C, c.m_conv)) L.m_conv_w = B.up(t->v);
+    if (auto t = B.get(d + "conv.b", C, -1)) L.m_conv_b = B.up(t->v);
+    if (auto t = B.get(d + "dt_bias", H, -1)) L.m_dt_bias = B.up_f32(t->v);
+    if (auto t = B.get(d + "A_log", H, -1)) L.m_A_log = B.up_f32(t->v);
+    if (auto t = B.get(d + "D", H, -1)) L.m_D = B.up_f32(t->v);
+    if (auto t = B.get(d + "norm", inner, -1)) L.m_norm = B.up_f32(t->v);
+    k_out = inner;
+    mx.in = std::max(mx.in, n_in); mx.cv = std::max(mx.cv, C); mx.f2 = std::max(mx.f2, inner);
+    if (dev_alloc(h, (void**)&L.conv_state, (size_t)rt.num_slots * (c.m_conv - 1) * C * 4, &h->bytes_state)) return HY_ERR_CUDA;
+    if (dev_alloc(h, (void**)&L.rec_state, (size_t)rt.num_slots * inner * c.m_state * 4, &h->bytes_state)) return HY_ERR_CUDA;
+  } else if (c.mixer == HY_MIX_LATENT) {
+    const int H = c.l_heads, R = c.l_kv_rank, rot = c.l_rot_dim, Dk = R + rot;
+    const bool own = c.l_kv_from < 0;
+    n_in = c.l_q_rank + (own ? Dk : 0);
+    stack_rows(win, B.get(d + "dq", c.l_q_rank, W));
+    if (own) stack_rows(win, B.get(d + "dkv", Dk, W));
+    if (auto t = B.get(d + "dq.norm", c.l_q_rank, -1)) L.l_qn = B.up_f32(t->v);
+    if (own) { if (auto t = B.get(d + "dkv.norm", R, -1)) L.l_kn = B.up_f32(t->v); }
+    const int nq = H * (c.l_dim + rot);
+    if (auto t = B.get(d + "uq", nq, c.l_q_rank)) { L.w_uq = B.up(t->v); L.w_uq_t = B.up_tiled(t->v, nq, c.l_q_rank); }
+    if (auto t = B.get(d + "uk", H * c.l_dim, R)) L.w_uk = B.up(t->v);
+    if (auto t = B.get(d + "uv", H * c.l_vdim, R)) {
+      std::vector<float> tr((size_t)H * R * c.l_vdim);           // [H][rank][vdim]
+      for (int hh = 0; hh < H; ++hh)
+        for (int j = 0; j < c.l_vdim; ++j)
+          for (int r = 0; r < R; ++r) tr[((size_t)hh * R + r) * c.l_vdim + j] = t->v[((size_t)hh * c.l_vdim + j) * R + r];
+      L.w_uvT = B.up(tr);
+    }
+    if (auto t = B.get(d + "sink", H, -1)) L.sink = B.up(t->v);
+    {
+      std::vector<double> f;
+      rotation_table(c, f, &L.rot.mag);
+      void* dv = nullptr;
+      if (dev_alloc(h, &dv, f.size() * 8, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
+      cudaMemcpy(dv, f.data(), f.size() * 8, cudaMemcpyHostToDevice);
+      L.rot.freq = (const double*)dv;
+      L.rot.pairs = (int)f.size();
+    }
+    k_out = H * c.l_vdim;
+    mx.f1 = std::max(mx.f1, n_in);
+    mx.cv = std::max(mx.cv, std::max(c.l_q_rank, H * Dk));
+    mx.in = std::max(mx.in, nq);
+    mx.f2 = std::max(mx.f2, H * R);
+    if (own) {
+      if (dev_alloc(h, &L.cache, (size_t)rt.num_pages * rt.page_size * Dk * h->esz(), &h->bytes_cache)) return HY_ERR_CUDA;
+    } else {
+      L.cache = h->lw[(size_t)c.l_kv_from].cache;
+    }
+  } else {
+    const int H = c.g_heads, nq = H * c.g_dim, nv = H * c.g_vdim;
+    n_in = 2 * nq + nv;
+    L.c_q = 0; L.c_k = nq; L.c_v = 2 * nq;
+    stack_rows(win, B.get(d + "q", nq, W));
+    stack_rows(win, B.get(d + "f", nq, W));
+    stack_rows(win, B.get(d + "v", nv, W));
+    if (auto t = B.get(d + "f.b", nq, -1)) L.g_fb = B.up_f32(t->v);
+    if (auto t = B.get(d + "lower", nq, -1)) L.g_lower = B.up_f32(t->v);
+    if (auto t = B.get(d + "norm", c.g_vdim, -1)) L.g_norm = B.up_f32(t->v);
+    k_out = nv;
+    mx.in = std::max(mx.in, n_in);
+    if (dev_alloc(h, (void**)&L.rec_state, (size_t)rt.num_slots * H * c.g_dim * c.g_vdim * 4, &h->bytes_state)) return HY_ERR_CUDA;
+  }
+  const HostTensor* wo = B.get(d + "o", W, k_out);
+  if (B.rc != HY_OK) return B.rc;
+  L.n_in = n_in; L.c_up = n_in;
+  L.w_in = B.up(win);
+  L.w_in_t = B.up_tiled(win, n_in, W);
+  L.k_out = k_out;
+  L.w_out = B.up(wo->v);
+  L.w_out_t = B.up_tiled(wo->v, W, k_out);
+  mx.out = std::max(mx.out, k_out);
+  if (c.ff_kind == HY_FF_ROUTED) {
+    tanh_norm_load(B, p + "norm2", W, &L.n2);
+    tanh_norm_load(B, p + "norm2b", W, &L.n2b);
+    if (auto t = B.get(p + "ls2", W, -1)) L.ls2 = B.up_f32(t->v);
+    const int E = c.x_experts, ff = c.ff;
+    if (auto t = B.get(p + "mlp.router", E, W)) L.w_router = B.up(t->v);
+    std::vector<float> gu, dn;
+    gu.reserve((size_t)E * 2 * ff * W);
+    dn.reserve((size_t)E * W * ff);
+    for (int e = 0; e < E && B.rc == HY_OK; ++e) {
+      const std::string x = p + "mlp.e" + std::to_string(e) + ".";
+      stack_rows(gu, B.get(x + "gate", ff, W));
+      stack_rows(gu, B.get(x + "up", ff, W));
+      stack_rows(dn, B.get(x + "down", W, ff));
+    }
+    if (B.rc != HY_OK) return B.rc;
+    L.w_gu = B.up(gu);
+    L.w_down = B.up(dn);
+    mx.f1 = std::max(mx.f1, E);
+    mx.in = std::max(mx.in, c.x_top * ((ff + 7) & ~7));
+    mx.f2 = std::max(mx.f2, c.x_top * W);
+  }
+  return B.rc;
+}
+
 // rows of several [n_i, k] matrices stacked
 void stack_rows(std::vector<float>& dst, const HostTensor* t) { if (t) dst.insert(dst.end(), t->v.begin(), t->v.end()); }
 
@@ -286,9 +493,10 @@ extern "C" int hy_finalize(hy_handle h) {
   const int W = h->m.width, V = h->m.vocab;
   const hy_runtime_cfg& rt = h->rt;
   if (auto t = B.get("embed", V, W)) h->embed = B.up(t->v);
-  if (auto t = B.get("final.norm", W, -1)) h->final_norm = B.up(t->v);
+  if (h->m.norm_kind == HY_NORM_TANH) tanh_norm_load(B, "final.norm", W, &h->final_tanh);
+  else if (auto t = B.get("final.norm", W, -1)) h->final_norm = B.up(t->v);
   if (auto t = B.get("head", V, W)) { h->head = B.up(t->v); h->head_t = B.up_tiled(t->v, V, W); }
-  {
+  if (h->m.pos_kind == HY_POS_SINUSOID) {
     std::vector<double> f((W + 1) / 2);
     for (size_t i = 0; i < f.size(); ++i) f[i] = pow(10000.0, -2.0 * (double)i / (double)W);
     void* d = nullptr;
@@ -298,9 +506,15 @@ extern "C" int hy_finalize(hy_handle h) {
   }
   h->lw.resize(h->lc.size());
   int max_in = 1, max_out = 1, max_cv = 1, max_f1 = 1, max_f2 = 1;
+  Maxima mx;
   for (size_t i = 0; i < h->lc.size() && B.rc == HY_OK; ++i) {
     const hy_layer_cfg& c = h->lc[i];
     LayerW& L = h->lw[i];
+    if (h->m.block_kind == HY_BLOCK_SANDWICH) {
+      const int rc = finalize_sandwich_layer(h, B, i, mx);
+      if (rc != HY_OK) return rc;
+      continue;
+    }
     const std::string p = "l" + std::to_string(i) + ".";
     if (auto t = B.get(p + "norm1", W, -1)) L.norm1 = B.up(t->v);
     const int ff = c.ff_kind == HY_FF_NONE ? 0 : c.ff;
@@ -396,6 +610,8 @@ extern "C" int hy_finalize(hy_handle h) {
   }
   if (B.rc != HY_OK) return B.rc;
   h->host.clear();
+  max_in = std::max(max_in, mx.in); max_out = std::max(max_out, mx.out); max_cv = std::max(max_cv, mx.cv);
+  max_f1 = std::max(max_f1, mx.f1); max_f2 = std::max(max_f2, mx.f2);
   // workspace
   const size_t T = (size_t)rt.max_step_tokens, es = h->esz();
   auto r8 = [](int v) { return (v + 7) & ~7; };
@@ -417,8 +633,10 @@ extern "C" int hy_finalize(hy_handle h) {
   HY_CUDA(cudaMallocHost((void**)&h->meta_h, h->meta_words * 4));
   if (h->m.dtype == HY_DTYPE_BF16) {
     int maxH = 0, maxG = 0, maxD = 0;
-    for (auto& c : h->lc)
+    for (auto& c : h->lc) {
       if (c.mixer == HY_MIX_ATTN_SCAN) { maxH = std::max(maxH, c.a_heads); maxG = std::max(maxG, c.a_kv_heads); maxD = std::max(maxD, c.a_dim); }
+      if (c.mixer == HY_MIX_LATENT) { maxH = std::max(maxH, c.l_heads); maxG = std::max(maxG, 1); maxD = std::max(maxD, c.l_kv_rank + c.l_rot_dim); }
+    }
     if (maxH > 0) {
       h->part_rows = std::max<size_t>(T * maxH, 4096);
       h->units_cap = h->part_rows / 64 + (size_t)rt.max_step_entries * maxG * 257 + 64;
@@ -426,6 +644,27 @@ extern "C" int hy_finalize(hy_handle h) {
       if (dev_alloc(h, (void**)&h->part_ml, h->part_rows * 2 * 4, &h->bytes_ws)) return HY_ERR_CUDA;
       if (dev_alloc(h, (void**)&h->units_d, h->units_cap * sizeof(AttnUnit), &h->bytes_ws)) return HY_ERR_CUDA;
       HY_CUDA(cudaMallocHost((void**)&h->units_h, h->units_cap * sizeof(AttnUnit)));
+    }
+  }
+  {
+    int maxE = 0, maxTop = 0;
+    for (auto& c : h->lc)
+      if (c.ff_kind == HY_FF_ROUTED) { maxE = std::max(maxE, c.x_experts); maxTop = std::max(maxTop, c.x_top); }
+    if (maxE > 0) {
+      const size_t P = T * (size_t)maxTop;
+      h->x_max_tiles = (int)(P / HY_XT) + maxE + 1;
+      if (dev_alloc(h, (void**)&h->x_ids, P * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->x_wts, P * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->x_row_tok, P * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->x_pair_row, P * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->x_counts, (size_t)maxE * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->x_offs, ((size_t)maxE + 1) * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->x_fill, (size_t)maxE * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->x_tile_e, (size_t)h->x_max_tiles * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->x_tile_r0, (size_t)h->x_max_tiles * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+      if (dev_alloc(h, (void**)&h->x_meta, 16, &h->bytes_ws)) return HY_ERR_CUDA;
+      HY_CUDA(cudaMemset(h->x_counts, 0, (size_t)maxE * 4));
+      HY_CUDA(cudaMemset(h->x_meta, 0, 16));
     }
   }
   if (dev_alloc(h, (void**)&h->err_d, 4, &h->bytes_ws)) return HY_ERR_CUDA;
@@ -530,6 +769,184 @@ bool attn_units(hy_engine* h, int E, int T, int H, int G) {
   return true;
 }
 
+
+// One layer of a norm - sublayer - norm model:  x += ls1 * n1b(mixer(n1(x)));  x += ls2 * n2b(experts(n2(x))).
+// The output norms are element-wise, so they run in the epilogue of the mixer's output projection and in the experts'
+// combine kernel, on the fp32 accumulators, together with the layer scale and the residual sum.
+template <typename AT>
+int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
+  typedef AT WT;
+  const hy_layer_cfg& c = h->lc[li];
+  const LayerW& L = h->lw[li];
+  const int W = h->m.width, T = b.T, E = b.E;
+  const float eps = h->m.norm_eps;
+  cudaStream_t s = h->stream;
+  AT* hb = (AT*)h->hbuf; AT* pin = (AT*)h->pin; AT* cat = (AT*)h->cat; AT* cv = (AT*)h->cv;
+  {
+    ProfScope ps(h, HY_PROF_NORM);
+    tanh_norm_kernel<AT><<<T, 256, 0, s>>>(h->x, nullptr, L.n1, W, hb);
+    h->launches++;
+  }
+  if (c.mixer == HY_MIX_SSD) {
+    const int H = c.m_heads, P = c.m_vdim, N = c.m_state, G = c.m_groups, inner = H * P, GN = G * N, C = inner + 2 * GN;
+    {
+      ProfScope ps(h, HY_PROF_GEMM_IN);
+      gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, to_buf(pin, h->ld_pin), L.w_in_t);
+    }
+    {
+      ProfScope ps(h, HY_PROF_CONV);
+      conv_kernel<AT, WT><<<dim3((C + 127) / 128, T), 128, 0, s>>>(b, pin, h->ld_pin, inner, C, c.m_conv, (const WT*)L.m_conv_w,
+                                                                   (const WT*)L.m_conv_b, 1, L.conv_state, cv, h->ld_cv);
+      conv_tail_kernel<AT><<<dim3((C + 127) / 128, E), 128, 0, s>>>(b, pin, h->ld_pin, inner, C, c.m_conv, L.conv_state);
+      h->launches += 2;
+    }
+    {
+      ProfScope ps(h, HY_PROF_SCAN);
+      const int nper = N <= 32 ? 1 : N <= 64 ? 2 : N <= 128 ? 4 : 8;
+      int lanes = 1;
+      while (lanes * nper < N) lanes <<= 1;
+      const int per_block = 128 / lanes, bph = (P + per_block - 1) / per_block;
+      dim3 grid(H * bph, E);
+      const size_t smem = (size_t)HY_SCAN_TB * (2 * N + per_block + 2) * 4;
+#define HY_SSD_ARGS b, cv, h->ld_cv, inner, inner + GN, pin + 2 * inner + 2 * GN, h->ld_pin, L.m_dt_bias, L.m_A_log, L.m_D, H, P, N, \
+      G, lanes, bph, L.rec_state, h->f2, h->ld_f2
+      if (nper == 1) ssd_scan_kernel<AT, 1><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
+      else if (nper == 2) ssd_scan_kernel<AT, 2><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
+      else if (nper == 4) ssd_scan_kernel<AT, 4><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
+      else ssd_scan_kernel<AT, 8><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
+#undef HY_SSD_ARGS
+      gated_group_norm_kernel<AT><<<dim3(T, c.m_norm_groups), 128, 0, s>>>(h->f2, h->ld_f2, pin, h->ld_pin, L.m_norm, inner,
+                                                                          c.m_norm_groups, eps, cat, h->ld_cat);
+      h->launches += 2;
+    }
+  } else if (c.mixer == HY_MIX_LATENT) {
+    const int H = c.l_heads, R = c.l_kv_rank, rot = c.l_rot_dim, Dk = R + rot, dn = c.l_dim, dv = c.l_vdim;
+    const int own = c.l_kv_from < 0 ? 1 : 0;
+    {
+      ProfScope ps(h, HY_PROF_GEMM_IN);
+      gemm<AT, WT, float>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, to_buf(h->f1, h->ld_f1), L.w_in_t);
+    }
+    {
+      ProfScope ps(h, HY_PROF_CONV);
+      latent_prep_kernel<AT><<<T, 128, (size_t)(2 * L.rot.pairs + 2) * 4, s>>>(b, h->f1, h->ld_f1, c.l_q_rank, R, rot, own, L.l_qn,
+                                                                               L.l_kn, eps, L.rot, cv, h->ld_cv, (AT*)L.cache);
+      h->launches++;
+    }
+    {
+      ProfScope ps(h, HY_PROF_SMALL_GEMM);
+      gemm<AT, WT, AT>(h, cv, h->ld_cv, (const WT*)L.w_uq, c.l_q_rank, T, H * (dn + rot), c.l_q_rank, to_buf(pin, h->ld_pin), L.w_uq_t);
+      latent_query_kernel<AT, WT><<<dim3((T + HY_LAT_TB - 1) / HY_LAT_TB, H, (R + 127) / 128), 128,
+                                    (size_t)(HY_LAT_TB * dn + 2 * L.rot.pairs + 2) * 4, s>>>(b, pin, h->ld_pin, (const WT*)L.w_uk, H, dn,
+                                                                                             rot, R, L.rot, cv, h->ld_cv);
+      h->launches++;
+    }
+    {
+      ProfScope ps(h, HY_PROF_ATTN);
+      bool tc = false;
+      if constexpr (std::is_same<AT, bf16>::value) {
+        if ((Dk == 32 || Dk == 64 || Dk == 128) && h->part_o && attn_units(h, E, T, H, 1)) {
+          tc = true;
+#define HY_ATTN_ARGS b, h->units_d, cv, h->ld_cv, (const bf16*)L.cache, H, 1, c.l_scale, 0.0f, 1, h->units_split, h->units_ns, R, \
+          h->part_o, h->part_ml
+          if (Dk == 32) attn_mma_kernel<32><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
+          else if (Dk == 64) attn_mma_kernel<64><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
+          else attn_mma_kernel<128><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
+#undef HY_ATTN_ARGS
+          attn_combine_kernel<WT, float><<<T * H, 64, 0, s>>>(b, h->part_o, h->part_ml, (const WT*)L.sink, nullptr, 0, H, Dk, R,
+                                                              h->units_split, h->units_ns, 1.0f, h->f2, h->ld_f2);
+          h->launches += 2;
+        }
+      }
+      if (!tc) {
+        attn_sink_kernel<AT, WT, float><<<(T * H + 3) / 4, 128, 4 * Dk * sizeof(float), s>>>(
+            b, cv, h->ld_cv, (const AT*)L.cache, (const WT*)L.sink, (const AT*)nullptr, 0, H, 1, Dk, R, c.l_scale, 0.0f, 1, 1.0f,
+            h->f2, h->ld_f2);
+        h->launches++;
+      }
+    }
+    {
+      ProfScope ps(h, HY_PROF_SMALL_GEMM);
+      latent_value_kernel<AT, WT><<<dim3((T + HY_LAT_TB - 1) / HY_LAT_TB, H, (dv + 127) / 128), 128, (size_t)HY_LAT_TB * R * 4, s>>>(
+          T, h->f2, h->ld_f2, (const WT*)L.w_uvT, H, R, dv, cat, h->ld_cat);
+      h->launches++;
+    }
+  } else {
+    const int H = c.g_heads, dk = c.g_dim, dv = c.g_vdim;
+    {
+      ProfScope ps(h, HY_PROF_GEMM_IN);
+      gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, to_buf(pin, h->ld_pin), L.w_in_t);
+    }
+    ProfScope ps(h, HY_PROF_DELTA);
+    static bool glr_attr = false;
+    if (!glr_attr) {
+      cudaFuncSetAttribute(glr_reg_kernel<AT, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      cudaFuncSetAttribute(glr_reg_kernel<AT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      cudaFuncSetAttribute(glr_reg_kernel<AT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      cudaFuncSetAttribute(glr_kernel<AT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+      glr_attr = true;
+    }
+#define HY_GLR_ARGS b, pin, h->ld_pin, L.c_q, L.c_k, L.c_v, L.g_fb, L.g_lower, L.g_norm, H, dk, dv, eps, L.rec_state, cat, h->ld_cat
+    const int nthr = std::max(((dv + 31) / 32) * 32, 32);
+    auto gsm = [](int dr, int nt) { return (size_t)HY_GLR_TB * (2 * dr + 2 * nt) * 4; };
+    if (dk <= 32 && nthr <= 512) glr_reg_kernel<AT, 32><<<dim3(H, E), nthr, gsm(32, nthr), s>>>(HY_GLR_ARGS);
+    else if (dk <= 64 && nthr <= 512) glr_reg_kernel<AT, 64><<<dim3(H, E), nthr, gsm(64, nthr), s>>>(HY_GLR_ARGS);
+    else if (dk <= 128 && nthr <= 256) glr_reg_kernel<AT, 128><<<dim3(H, E), nthr, gsm(128, nthr), s>>>(HY_GLR_ARGS);
+    else glr_kernel<AT><<<dim3(H, E), 256, ((size_t)dk * dv + 2 * dk + dv + 40) * 4, s>>>(HY_GLR_ARGS);
+#undef HY_GLR_ARGS
+    h->launches++;
+  }
+  {
+    ProfScope ps(h, HY_PROF_GEMM_OUT);
+    GemmOut o{nullptr, 0, 0, nullptr, 0, 0, h->x, W, 1.0f, L.n1b.w, L.n1b.b, L.ls1, L.n1b.alpha};
+    gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_out, L.k_out, T, W, L.k_out, o, L.w_out_t);
+  }
+  if (c.ff_kind != HY_FF_ROUTED) return HY_OK;
+  const int NE = c.x_experts, top = c.x_top, ff = c.ff, P = T * top, ldh = (ff + 7) & ~7;
+  {
+    ProfScope ps(h, HY_PROF_NORM);
+    tanh_norm_kernel<AT><<<T, 256, 0, s>>>(h->x, nullptr, L.n2, W, hb);
+    h->launches++;
+  }
+  const bool few = P <= 32;
+  {
+    ProfScope ps(h, HY_PROF_ROUTE);
+    gemm<AT, WT, float>(h, hb, W, (const WT*)L.w_router, W, T, NE, W, to_buf(h->f1, h->ld_f1));
+    const RouteCfg rc{NE, top, c.x_groups, c.x_keep, c.x_scale};
+    route_kernel<<<T, 32, (size_t)(NE + c.x_groups) * 4, s>>>(h->f1, h->ld_f1, rc, h->x_ids, h->x_wts, few ? nullptr : h->x_counts);
+    h->launches++;
+    if (!few) {
+      route_offsets_kernel<<<1, 32, 0, s>>>(h->x_counts, NE, h->x_offs, h->x_fill, h->x_tile_e, h->x_tile_r0, h->x_meta);
+      route_scatter_kernel<<<(P + 255) / 256, 256, 0, s>>>(P, top, h->x_ids, h->x_offs, h->x_fill, h->x_row_tok, h->x_pair_row);
+      h->launches += 2;
+    }
+  }
+  {
+    ProfScope ps(h, HY_PROF_EXPERTS);
+    float* ys = h->f2;                                        // [pairs, width] fp32
+    if (few) {
+      static bool rows_attr = false;
+      if (!rows_attr) {
+        cudaFuncSetAttribute(expert_rows_kernel<AT, WT, AT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(expert_rows_kernel<AT, WT, float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        rows_attr = true;
+      }
+      expert_rows_kernel<AT, WT, AT, true><<<dim3(std::min((ff + 7) / 8, 256), P), 256, (size_t)W * sizeof(AT), s>>>(
+          hb, W, h->x_ids, top, 1, (const WT*)L.w_gu, (size_t)2 * ff * W, ff, W, pin, ldh);
+      expert_rows_kernel<AT, WT, float, false><<<dim3(std::min((W + 7) / 8, 256), P), 256, (size_t)ff * sizeof(AT), s>>>(
+          pin, ldh, h->x_ids, top, 0, (const WT*)L.w_down, (size_t)W * ff, W, ff, ys, W);
+    } else {
+      const int tiles = std::min(h->x_max_tiles, P / HY_XT + NE + 1);
+      expert_gemm_simt_kernel<AT, WT, AT, true><<<dim3((ff + 63) / 64, tiles), 256, 0, s>>>(
+          hb, W, h->x_row_tok, (const WT*)L.w_gu, (size_t)2 * ff * W, ff, W, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, pin, ldh);
+      expert_gemm_simt_kernel<AT, WT, float, false><<<dim3((W + 63) / 64, tiles), 256, 0, s>>>(
+          pin, ldh, nullptr, (const WT*)L.w_down, (size_t)W * ff, W, ff, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, ys, W);
+    }
+    expert_combine_kernel<<<T, 256, 0, s>>>(ys, W, few ? nullptr : h->x_pair_row, h->x_wts, top, W, L.n2b, L.ls2, h->x);
+    h->launches += 3;
+  }
+  return HY_OK;
+}
+
 template <typename AT>
 int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float* layers_out) {
   typedef AT WT;
@@ -545,6 +962,11 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
   for (size_t li = 0; li < h->lc.size(); ++li) {
     const hy_layer_cfg& c = h->lc[li];
     const LayerW& L = h->lw[li];
+    if (h->m.block_kind == HY_BLOCK_SANDWICH) {
+      sandwich_layer<AT>(h, b, li);
+      if (layers_out) cudaMemcpyAsync(layers_out + li * (size_t)T * W, h->x, (size_t)T * W * 4, cudaMemcpyDeviceToHost, s);
+      continue;
+    }
     const int ff = c.ff_kind == HY_FF_NONE ? 0 : c.ff;
     {
       ProfScope ps(h, HY_PROF_NORM);
@@ -575,19 +997,19 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
         if ((c.a_dim == 32 || c.a_dim == 64 || c.a_dim == 128) && h->part_o && attn_units(h, E, T, c.a_heads, c.a_kv_heads)) {
           tc = true;
 #define HY_ATTN_ARGS b, h->units_d, cv, h->ld_cv, (const bf16*)L.cache, c.a_heads, c.a_kv_heads, c.a_scale, c.a_qt_coef, \
-          c.a_qt_every, h->units_split, h->units_ns, h->part_o, h->part_ml
+          c.a_qt_every, h->units_split, h->units_ns, c.a_dim, h->part_o, h->part_ml
           if (c.a_dim == 32) attn_mma_kernel<32><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
           else if (c.a_dim == 64) attn_mma_kernel<64><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
           else attn_mma_kernel<128><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
 #undef HY_ATTN_ARGS
-          attn_combine_kernel<WT><<<T * c.a_heads, 64, 0, s>>>(b, h->part_o, h->part_ml, (const WT*)L.sink, pin + L.c_g, h->ld_pin,
-              c.a_heads, c.a_dim, h->units_split, h->units_ns, c.left_scale, cat + L.o_mix, h->ld_cat);
+          attn_combine_kernel<WT, bf16><<<T * c.a_heads, 64, 0, s>>>(b, h->part_o, h->part_ml, (const WT*)L.sink, pin + L.c_g, h->ld_pin,
+              c.a_heads, c.a_dim, c.a_dim, h->units_split, h->units_ns, c.left_scale, cat + L.o_mix, h->ld_cat);
           h->launches++;
         }
       }
       if (!tc)
-      attn_sink_kernel<AT, WT><<<(T * c.a_heads + 3) / 4, 128, 4 * c.a_dim * sizeof(float), s>>>(
-          b, cv, h->ld_cv, (const AT*)L.cache, (const WT*)L.sink, pin + L.c_g, h->ld_pin, c.a_heads, c.a_kv_heads, c.a_dim,
+      attn_sink_kernel<AT, WT, AT><<<(T * c.a_heads + 3) / 4, 128, 4 * c.a_dim * sizeof(float), s>>>(
+          b, cv, h->ld_cv, (const AT*)L.cache, (const WT*)L.sink, pin + L.c_g, h->ld_pin, c.a_heads, c.a_kv_heads, c.a_dim, c.a_dim,
           c.a_scale, c.a_qt_coef, c.a_qt_every, c.left_scale, cat + L.o_mix, h->ld_cat);
       }
       h->launches += 4;
@@ -680,7 +1102,8 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
   }
   if (n_want > 0) {
     ProfScope ps(h, HY_PROF_HEAD);
-    rmsnorm_kernel<WT, AT><<<n_want, 256, 0, s>>>(h->x, want_d, (const WT*)h->final_norm, eps, W, (AT*)h->hw);
+    if (h->m.norm_kind == HY_NORM_TANH) tanh_norm_kernel<AT><<<n_want, 256, 0, s>>>(h->x, want_d, h->final_tanh, W, (AT*)h->hw);
+    else rmsnorm_kernel<WT, AT><<<n_want, 256, 0, s>>>(h->x, want_d, (const WT*)h->final_norm, eps, W, (AT*)h->hw);
     h->launches++;
     GemmOut o = to_buf(h->logits, h->m.vocab);
     o.alpha = h->m.logit_scale;

@@ -67,6 +67,7 @@ struct Batch {
 // ---- embedding: table row times a scale, plus the sinusoid of the position ----------------------------------------------
 // entry 2i = sin(p f_i), entry 2i+1 = cos(p f_i); f_i = 10000^(-2i / width) comes from a host-made fp64 table and the angle
 // is formed and reduced in fp64 (at position 1000 an fp32 angle is already 6e-5 off), the result enters the fp32 stream.
+// inv_freq == NULL: no positional term (designs whose positions enter through a rotation inside attention).
 template <typename WT>
 __global__ void embed_kernel(Batch b, const WT* __restrict__ table, const double* __restrict__ inv_freq, float scale,
                              int width, float* __restrict__ x) {
@@ -74,10 +75,25 @@ __global__ void embed_kernel(Batch b, const WT* __restrict__ table, const double
   const int tok = b.tok[t];
   const double p = (double)b.tok_pos[t];
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    const double ang = p * inv_freq[c >> 1];
-    const float pe = (float)((c & 1) ? cos(ang) : sin(ang));
+    float pe = 0.0f;
+    if (inv_freq) {
+      const double ang = p * inv_freq[c >> 1];
+      pe = (float)((c & 1) ? cos(ang) : sin(ang));
+    }
     x[(size_t)t * width + c] = to_f(table[(size_t)tok * width + c]) * scale + pe;
   }
+}
+
+// ---- element-wise tanh norm: tanh(alpha x) w + b, no statistics ------------------------------------------------------------
+// rows: NULL = row r of x, else x row rows[r].  Parameters are fp32.
+struct TanhNorm { const float* w; const float* b; float alpha; };
+template <typename OT>
+__global__ void tanh_norm_kernel(const float* __restrict__ x, const int* __restrict__ rows, TanhNorm n, int width,
+                                 OT* __restrict__ out) {
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[(size_t)r * width + c] = from_f<OT>(fmaf(tanhf(n.alpha * xr[c]), n.w[c], n.b[c]));
 }
 
 // ---- RMS norm with a weight stored as an offset from one (plain = 0: multiply by w itself) ------------------------------
@@ -99,16 +115,23 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 // ---- generic matrix product C[t, n] = sum_k A[t, k] W[n, k], fp32 accumulation in k order -----------------------------------
 // Destinations: resid != NULL: resid[t, n] += alpha * c (fp32, the residual stream).  Otherwise columns < split go to
 // out1[t * ld1 + n], columns >= split to out2[t * ld2 + n - split], squared ReLU first when act2 (the feed-forward's
-// hidden activation leaves the merged input projection already activated).
+// hidden activation leaves the merged input projection already activated).  With post_w set, the residual receives
+// post_ls[n] * (tanh(post_alpha c) post_w[n] + post_b[n]): a sublayer's output norm (element-wise, so it needs no second
+// pass) and its layer scale, applied to the fp32 accumulator.
 struct GemmOut {
   void* out1; int ld1; int split; void* out2; int ld2; int act2;
   float* resid; int ldr; float alpha;
+  const float* post_w; const float* post_b; const float* post_ls; float post_alpha;
 };
 
 template <typename TO>
 __device__ __forceinline__ void gemm_store(const GemmOut& o, int t, int n, float c) {
   c *= o.alpha;
-  if (o.resid) { o.resid[(size_t)t * o.ldr + n] += c; return; }
+  if (o.resid) {
+    if (o.post_w) c = o.post_ls[n] * fmaf(tanhf(o.post_alpha * c), o.post_w[n], o.post_b[n]);
+    o.resid[(size_t)t * o.ldr + n] += c;
+    return;
+  }
   if (n < o.split) { ((TO*)o.out1)[(size_t)t * o.ld1 + n] = from_f<TO>(c); return; }
   if (o.act2) { c = fmaxf(c, 0.0f); c = c * c; }
   ((TO*)o.out2)[(size_t)t * o.ld2 + (n - o.split)] = from_f<TO>(c);
@@ -315,13 +338,15 @@ __global__ void cache_append_kernel(Batch b, const AT* __restrict__ k, int ldk, 
 // ---- causal softmax attention with a sink; values are the keys -----------------------------------------------------------------
 // One warp per (token, query head).  Keys are walked in groups of 32 aligned to absolute positions; the running maximum
 // starts at the sink logit and the denominator at exp(sink - sink) = 1: the sink has no key and no value.  The query is
-// multiplied by its position's temperature in fp32.  Output: heads concatenated, times sigmoid(gate), times out_scale.
-constexpr int HY_ATT_MAXD = 8;      // dims per lane: dim <= 256
-template <typename AT, typename WT>
+// multiplied by its position's temperature in fp32.  The value of a key is its first vdim dimensions (vdim == dim: the
+// values are the keys; vdim < dim: a latent followed by a part that only enters the score).  Output: heads concatenated
+// [H, vdim], times sigmoid(gate) when there is a gate, times out_scale.
+constexpr int HY_ATT_MAXD = 20;     // dims per lane: dim <= 640
+template <typename AT, typename WT, typename OT>
 __global__ void __launch_bounds__(128) attn_sink_kernel(Batch b, const AT* __restrict__ q, int ldq, const AT* __restrict__ cache,
                                                         const WT* __restrict__ sink, const AT* __restrict__ gate, int ldg,
-                                                        int H, int G, int dim, float scale, float qt_coef, int qt_every,
-                                                        float out_scale, AT* __restrict__ out, int ldo) {
+                                                        int H, int G, int dim, int vdim, float scale, float qt_coef,
+                                                        int qt_every, float out_scale, OT* __restrict__ out, int ldo) {
   extern __shared__ __align__(16) unsigned char hy_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* qs = reinterpret_cast<float*>(hy_smem) + warp * dim;
@@ -363,7 +388,7 @@ __global__ void __launch_bounds__(128) attn_sink_kernel(Batch b, const AT* __res
 #pragma unroll
       for (int i = 0; i < HY_ATT_MAXD; ++i) {
         const int d = lane + 32 * i;
-        if (d < dim) acc[i] = fmaf(pj, to_f(kj[d]), acc[i]);
+        if (d < vdim) acc[i] = fmaf(pj, to_f(kj[d]), acc[i]);
       }
     }
   }
@@ -371,9 +396,9 @@ __global__ void __launch_bounds__(128) attn_sink_kernel(Batch b, const AT* __res
 #pragma unroll
   for (int i = 0; i < HY_ATT_MAXD; ++i) {
     const int d = lane + 32 * i;
-    if (d < dim) {
-      const float gt = sigmoid_f(to_f(gate[(size_t)t * ldg + h * dim + d]));
-      out[(size_t)t * ldo + h * dim + d] = from_f<AT>(acc[i] * inv * gt * out_scale);
+    if (d < vdim) {
+      const float gt = gate ? sigmoid_f(to_f(gate[(size_t)t * ldg + h * vdim + d])) : 1.0f;
+      out[(size_t)t * ldo + h * vdim + d] = from_f<OT>(acc[i] * inv * gt * out_scale);
     }
   }
 }

@@ -1,0 +1,365 @@
+// hy_mixers.cuh — device kernels of three more mixers of the layered hybrid decoders (libjf_hybrid.so):
+//   * a state-space recurrence with ONE decay per head (the scalar-decay form of the selective scan) and its gated,
+//     grouped output norm;
+//   * attention over a shared low-rank latent: the cache holds, per token, the normed latent and one rotated key part that
+//     all heads share.  The per-head key up-projection is folded into the query and the value up-projection is applied
+//     after the weighted sum, so attention itself runs over the cache rows as they are: one "key head" of size
+//     rank + rot whose first `rank` dimensions are also the values (the sink-attention kernels serve it);
+//   * a gated linear recurrence whose forget gate, bounded below per channel, also sets what is written.
+// Same precision rule as hy_kernels.cuh: norms, angles, decays, gates, step sizes and states are fp32 (angles fp64).
+#pragma once
+#include "hy_kernels.cuh"
+
+namespace hy {
+
+// ---- rotation of dimension pairs (2i, 2i + 1) -------------------------------------------------------------------------
+// Frequencies come from a host-made fp64 table (any interpolation of the frequencies is already in it); the angle is
+// formed and reduced in fp64, cosine and sine are multiplied by `mag` and enter the fp32 computation.
+struct Rotation { const double* freq; int pairs; float mag; };
+
+__device__ __forceinline__ void rotation_row(const Rotation& r, int pos, float* cs /* [2 * pairs] in shared memory */) {
+  for (int i = threadIdx.x; i < r.pairs; i += blockDim.x) {
+    double s, c;
+    sincos((double)pos * r.freq[i], &s, &c);
+    cs[2 * i] = (float)c * r.mag;
+    cs[2 * i + 1] = (float)s * r.mag;
+  }
+}
+
+// ---- state-space recurrence, one decay per head ----------------------------------------------------------------------------
+// Per head h (group g = h / (heads / groups)), channel p, state n:
+//   dt = softplus(dt_raw_h + dt_bias_h) ; S[p, n] <- exp(-exp(A_log_h) dt) S[p, n] + dt x_p B_n ; y_p = sum_n S[p, n] C_n + D_h x_p
+// L lanes (a power of two) share a channel, each holding NPER states.  xbc [T, ldx]: x at column 0 (heads * vdim), B at
+// col_b, C at col_c (groups * nstate each), after convolution and activation.  state [slot][heads * vdim][nstate] fp32.
+// y leaves in fp32 (it enters a norm).  Inputs of HY_SCAN_TB tokens are staged per block; a block's channels lie in one head.
+template <typename AT, int NPER>
+__global__ void __launch_bounds__(128) ssd_scan_kernel(Batch b, const AT* __restrict__ xbc, int ldx, int col_b, int col_c,
+                                                       const AT* __restrict__ dt_raw, int lddt, const float* __restrict__ dt_bias,
+                                                       const float* __restrict__ A_log, const float* __restrict__ D, int heads,
+                                                       int vdim, int nstate, int groups, int L, int blocks_per_head,
+                                                       float* __restrict__ state, float* __restrict__ y, int ldy) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  const int e = blockIdx.y;
+  const int per_block = blockDim.x / L;
+  float* sB = reinterpret_cast<float*>(hy_smem);              // [TB][nstate]
+  float* sC = sB + HY_SCAN_TB * nstate;                       // [TB][nstate]
+  float* sx = sC + HY_SCAN_TB * nstate;                       // [TB][per_block]
+  float* sdt = sx + HY_SCAN_TB * per_block;                   // [TB]
+  float* sdec = sdt + HY_SCAN_TB;                             // [TB]
+  const int h = blockIdx.x / blocks_per_head;
+  const int p0 = (blockIdx.x % blocks_per_head) * per_block;
+  const int g = h / (heads / groups);
+  const int cl = threadIdx.x / L, sub = threadIdx.x % L;
+  const int p = p0 + cl;
+  const bool live = p < vdim;
+  const int pc = live ? p : vdim - 1;
+  const int start = b.ent_start[e], cnt = b.ent_start[e + 1] - start, pos0 = b.ent_pos0[e];
+  float* st = state + (((size_t)b.ent_slot[e] * heads + h) * vdim + pc) * nstate;
+  float S[NPER];
+#pragma unroll
+  for (int i = 0; i < NPER; ++i) {
+    const int n = sub + i * L;
+    S[i] = (n < nstate && pos0 > 0) ? st[n] : 0.0f;
+  }
+  const float rate = expf(A_log[h]), dd = D[h], bias = dt_bias[h];
+  for (int j0 = 0; j0 < cnt; j0 += HY_SCAN_TB) {
+    const int nb = min(HY_SCAN_TB, cnt - j0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb * nstate; i += blockDim.x) {
+      const int tt = i / nstate, n = i % nstate;
+      const size_t row = (size_t)(start + j0 + tt) * ldx;
+      sB[tt * nstate + n] = to_f(xbc[row + col_b + g * nstate + n]);
+      sC[tt * nstate + n] = to_f(xbc[row + col_c + g * nstate + n]);
+    }
+    for (int i = threadIdx.x; i < nb * per_block; i += blockDim.x) {
+      const int tt = i / per_block, k = i % per_block;
+      sx[i] = to_f(xbc[(size_t)(start + j0 + tt) * ldx + h * vdim + min(p0 + k, vdim - 1)]);
+    }
+    if (threadIdx.x < nb) {
+      const float dt = softplus_f(to_f(dt_raw[(size_t)(start + j0 + threadIdx.x) * lddt + h]) + bias);
+      sdt[threadIdx.x] = dt;
+      sdec[threadIdx.x] = expf(-rate * dt);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nb; ++tt) {
+      const float dt = sdt[tt], dec = sdec[tt], xv = sx[tt * per_block + cl];
+      const float dx = dt * xv;
+      float acc = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NPER; ++i) {
+        const int n = sub + i * L;
+        if (n < nstate) {
+          S[i] = fmaf(dec, S[i], dx * sB[tt * nstate + n]);
+          acc = fmaf(S[i], sC[tt * nstate + n], acc);
+        }
+      }
+      for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (live && sub == 0) y[(size_t)(start + j0 + tt) * ldy + h * vdim + p] = fmaf(dd, xv, acc);
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) {
+      const int n = sub + i * L;
+      if (n < nstate) st[n] = S[i];
+    }
+  }
+}
+
+// Gate, then norm: v = y silu(z); each of `parts` equal slices of a row is divided by its own root mean square; times w.
+template <typename AT>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, int ldy, const AT* __restrict__ z, int ldz,
+                                        const float* __restrict__ w, int inner, int parts, float eps, AT* __restrict__ out,
+                                        int ldo) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, part = blockIdx.y, n = inner / parts, c0 = part * n;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float v = y[(size_t)t * ldy + c0 + c] * silu_f(to_f(z[(size_t)t * ldz + c0 + c]));
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float v = y[(size_t)t * ldy + c0 + c] * silu_f(to_f(z[(size_t)t * ldz + c0 + c]));
+    out[(size_t)t * ldo + c0 + c] = from_f<AT>(v * inv * w[c0 + c]);
+  }
+}
+
+// ---- attention over a shared latent -------------------------------------------------------------------------------------------
+// After the merged down-projections (fp32, [query latent | key/value latent | raw rotated key part]):
+//   query latent  -> RMS norm, weight, into cq (operand of the query up-projection);
+//   key latent    -> RMS norm, weight, into the token's cache row, dimensions [0, rank);
+//   rotated part  -> rotation at the token's position, into the cache row, dimensions [rank, rank + rot).
+// A layer that borrows another layer's cache has no key part (own_kv = 0).  Cache: [page][slot in page][rank + rot].
+template <typename AT>
+__global__ void latent_prep_kernel(Batch b, const float* __restrict__ d, int ldd, int q_rank, int rank, int rot, int own_kv,
+                                   const float* __restrict__ qn_w, const float* __restrict__ kn_w, float eps, Rotation r,
+                                   AT* __restrict__ cq, int ldq, AT* __restrict__ cache) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  float* cs = reinterpret_cast<float*>(hy_smem);              // [2 * pairs]
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const float* row = d + (size_t)t * ldd;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
+  ss = block_sum(ss, red);
+  float inv = 1.0f / sqrtf(ss / (float)q_rank + eps);
+  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) cq[(size_t)t * ldq + c] = from_f<AT>(row[c] * inv * qn_w[c]);
+  if (!own_kv) return;
+  const int e = b.tok_ent[t], pos = b.tok_pos[t];
+  AT* dst = cache + ((size_t)b.pages[(size_t)e * b.max_pages + pos / b.page_size] * b.page_size + pos % b.page_size) * (rank + rot);
+  const float* kr = row + q_rank;
+  ss = 0.0f;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) ss = fmaf(kr[c], kr[c], ss);
+  ss = block_sum(ss, red);
+  inv = 1.0f / sqrtf(ss / (float)rank + eps);
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = from_f<AT>(kr[c] * inv * kn_w[c]);
+  rotation_row(r, pos, cs);
+  __syncthreads();
+  const float* kp = kr + rank;
+  for (int i = threadIdx.x; i < rot; i += blockDim.x) {
+    float v = kp[i];
+    if (i < 2 * r.pairs) {
+      const float c = cs[i & ~1], s = cs[i | 1];
+      v = (i & 1) ? fmaf(kp[i], c, kp[i - 1] * s) : fmaf(kp[i], c, -kp[i + 1] * s);
+    }
+    dst[rank + i] = from_f<AT>(v);
+  }
+}
+
+// The query as the cache rows want it: per (token, head)  [ W_uk_h^T q_unrotated  (rank) | rotated q part (rot) ].
+// q [T, ldq] holds heads of [dim | rot]; w_uk [H * dim, rank] row-major (thread r walks a column: coalesced across r).
+// A block serves HY_LAT_TB tokens of one head and 128 output dimensions, so a weight element is read once per 8 tokens.
+constexpr int HY_LAT_TB = 8;
+template <typename AT, typename WT>
+__global__ void __launch_bounds__(128) latent_query_kernel(Batch b, const AT* __restrict__ q, int ldq, const WT* __restrict__ w_uk,
+                                                           int H, int dim, int rot, int rank, Rotation r, AT* __restrict__ out,
+                                                           int ldo) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  float* qs = reinterpret_cast<float*>(hy_smem);              // [TB][dim]
+  float* cs = qs + HY_LAT_TB * dim;                           // [2 * pairs] of one token at a time
+  const int t0 = blockIdx.x * HY_LAT_TB, h = blockIdx.y, nb = min(HY_LAT_TB, b.T - t0);
+  for (int i = threadIdx.x; i < HY_LAT_TB * dim; i += blockDim.x) {
+    const int tt = i / dim, k = i % dim;
+    qs[i] = tt < nb ? to_f(q[(size_t)(t0 + tt) * ldq + h * (dim + rot) + k]) : 0.0f;
+  }
+  __syncthreads();
+  const int c = blockIdx.z * blockDim.x + threadIdx.x;
+  if (c < rank) {
+    float acc[HY_LAT_TB];
+#pragma unroll
+    for (int tt = 0; tt < HY_LAT_TB; ++tt) acc[tt] = 0.0f;
+    const WT* wc = w_uk + (size_t)h * dim * rank + c;
+    for (int k = 0; k < dim; ++k) {
+      const float w = to_f(wc[(size_t)k * rank]);
+#pragma unroll
+      for (int tt = 0; tt < HY_LAT_TB; ++tt) acc[tt] = fmaf(qs[tt * dim + k], w, acc[tt]);
+    }
+    for (int tt = 0; tt < nb; ++tt) out[(size_t)(t0 + tt) * ldo + h * (rank + rot) + c] = from_f<AT>(acc[tt]);
+  }
+  if (blockIdx.z != 0) return;
+  for (int tt = 0; tt < nb; ++tt) {
+    __syncthreads();
+    rotation_row(r, b.tok_pos[t0 + tt], cs);
+    __syncthreads();
+    const AT* qp = q + (size_t)(t0 + tt) * ldq + h * (dim + rot) + dim;
+    for (int i = threadIdx.x; i < rot; i += blockDim.x) {
+      float v = to_f(qp[i]);
+      if (i < 2 * r.pairs) {
+        const float cc = cs[i & ~1], ss = cs[i | 1];
+        v = (i & 1) ? fmaf(v, cc, to_f(qp[i - 1]) * ss) : fmaf(v, cc, -to_f(qp[i + 1]) * ss);
+      }
+      out[(size_t)(t0 + tt) * ldo + h * (rank + rot) + rank + i] = from_f<AT>(v);
+    }
+  }
+}
+
+// The value up-projection behind the weighted sum: out[t, h, j] = sum_r w_uvT[h][r][j] o[t, h, r]  (o fp32: the weighted
+// sum of latents; w_uvT is the value up-projection transposed per head at load so that thread j reads coalesced).
+template <typename AT, typename WT>
+__global__ void __launch_bounds__(128) latent_value_kernel(int T, const float* __restrict__ o, int ldi, const WT* __restrict__ w_uvT,
+                                                           int H, int rank, int vdim, AT* __restrict__ out, int ldo) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  float* os = reinterpret_cast<float*>(hy_smem);              // [TB][rank]
+  const int t0 = blockIdx.x * HY_LAT_TB, h = blockIdx.y, nb = min(HY_LAT_TB, T - t0);
+  for (int i = threadIdx.x; i < HY_LAT_TB * rank; i += blockDim.x) {
+    const int tt = i / rank, k = i % rank;
+    os[i] = tt < nb ? o[(size_t)(t0 + tt) * ldi + h * rank + k] : 0.0f;
+  }
+  __syncthreads();
+  const int j = blockIdx.z * blockDim.x + threadIdx.x;
+  if (j >= vdim) return;
+  float acc[HY_LAT_TB];
+#pragma unroll
+  for (int tt = 0; tt < HY_LAT_TB; ++tt) acc[tt] = 0.0f;
+  const WT* wc = w_uvT + (size_t)h * rank * vdim + j;
+  for (int k = 0; k < rank; ++k) {
+    const float w = to_f(wc[(size_t)k * vdim]);
+#pragma unroll
+    for (int tt = 0; tt < HY_LAT_TB; ++tt) acc[tt] = fmaf(os[tt * rank + k], w, acc[tt]);
+  }
+  for (int tt = 0; tt < nb; ++tt) out[(size_t)(t0 + tt) * ldo + h * vdim + j] = from_f<AT>(acc[tt]);
+}
+
+// ---- gated linear recurrence ------------------------------------------------------------------------------------------------------
+// Per head, S [dim, vdim]:  f = lower + (1 - lower) sigmoid(f_raw + f_bias)  (per key channel)
+//   S <- diag(f) S + (1 - f) v^T ; o = S^T silu(q_raw) ; out = o / rms(o) * norm_w  (norm over the head's vdim).
+// in [T, ld]: q_raw at col_q, f_raw at col_f (heads * dim each), v at col_v (heads * vdim).  state [slot][H][dim][vdim].
+// Thread j keeps column j of S in registers (key size <= DR); inputs of HY_GLR_TB tokens are staged by the block, the
+// output norms of the batch are made by one warp per token.
+constexpr int HY_GLR_TB = 16;
+template <typename AT, int DR>
+__global__ void __launch_bounds__(DR > 64 ? 256 : 512)
+glr_reg_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_f, int col_v, const float* __restrict__ f_bias,
+               const float* __restrict__ lower, const float* __restrict__ norm_w, int H, int dim, int vdim, float eps,
+               float* __restrict__ state, AT* __restrict__ out, int ldo) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  const int nt = blockDim.x, nwarps = nt >> 5;
+  float* sq = reinterpret_cast<float*>(hy_smem);               // [TB][DR] activated queries
+  float* sf = sq + HY_GLR_TB * DR;                             // [TB][DR] forget gates
+  float* sv = sf + HY_GLR_TB * DR;                             // [TB][nt] values
+  float* so = sv + HY_GLR_TB * nt;                             // [TB][nt] raw read-outs
+  const int h = blockIdx.x, e = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int start = b.ent_start[e], cnt = b.ent_start[e + 1] - start, pos0 = b.ent_pos0[e];
+  float* st = state + ((size_t)b.ent_slot[e] * H + h) * dim * vdim;
+  const bool col = tid < vdim;
+  float S[DR];
+#pragma unroll
+  for (int i = 0; i < DR; ++i) S[i] = (col && i < dim && pos0 > 0) ? st[(size_t)i * vdim + tid] : 0.0f;
+  for (int j0 = 0; j0 < cnt; j0 += HY_GLR_TB) {
+    const int nb = min(HY_GLR_TB, cnt - j0);
+    __syncthreads();
+    for (int i = tid; i < nb * DR; i += nt) {
+      const int tt = i / DR, k = i % DR;
+      const size_t t = (size_t)(start + j0 + tt);
+      const bool ok = k < dim;
+      sq[i] = ok ? silu_f(to_f(in[t * ld + col_q + h * dim + k])) : 0.0f;
+      const float lo = ok ? lower[h * dim + k] : 0.0f;
+      sf[i] = ok ? fmaf(1.0f - lo, sigmoid_f(to_f(in[t * ld + col_f + h * dim + k]) + f_bias[h * dim + k]), lo) : 1.0f;
+    }
+    for (int i = tid; i < nb * nt; i += nt) {
+      const int tt = i / nt, k = i % nt;
+      sv[i] = k < vdim ? to_f(in[(size_t)(start + j0 + tt) * ld + col_v + h * vdim + k]) : 0.0f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nb; ++tt) {
+      const float* fs = sf + tt * DR;
+      const float* qs = sq + tt * DR;
+      const float v = sv[tt * nt + tid];
+      float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < DR; i += 4) {
+        const float4 f4 = *reinterpret_cast<const float4*>(&fs[i]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[i]);
+        S[i] = fmaf(f4.x, S[i], (1.0f - f4.x) * v); S[i + 1] = fmaf(f4.y, S[i + 1], (1.0f - f4.y) * v);
+        S[i + 2] = fmaf(f4.z, S[i + 2], (1.0f - f4.z) * v); S[i + 3] = fmaf(f4.w, S[i + 3], (1.0f - f4.w) * v);
+        p0 = fmaf(S[i], q4.x, p0); p1 = fmaf(S[i + 1], q4.y, p1);
+        p2 = fmaf(S[i + 2], q4.z, p2); p3 = fmaf(S[i + 3], q4.w, p3);
+      }
+      so[tt * nt + tid] = (p0 + p1) + (p2 + p3);
+    }
+    __syncthreads();
+    for (int tt = warp; tt < nb; tt += nwarps) {
+      float o2 = 0.0f;
+      for (int k = lane; k < vdim; k += 32) o2 = fmaf(so[tt * nt + k], so[tt * nt + k], o2);
+      o2 = warp_sum(o2);
+      const float inv = 1.0f / sqrtf(o2 / (float)vdim + eps);
+      for (int k = lane; k < vdim; k += 32)
+        out[(size_t)(start + j0 + tt) * ldo + h * vdim + k] = from_f<AT>(so[tt * nt + k] * inv * norm_w[k]);
+    }
+  }
+  if (col) {
+#pragma unroll
+    for (int i = 0; i < DR; ++i)
+      if (i < dim) st[(size_t)i * vdim + tid] = S[i];
+  }
+}
+
+// The same recurrence for any head size whose state fits shared memory: S [dim][vdim] in shared memory, a thread walks
+// the columns j = tid, tid + blockDim, ...; one token at a time.
+template <typename AT>
+__global__ void __launch_bounds__(256)
+glr_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_f, int col_v, const float* __restrict__ f_bias,
+           const float* __restrict__ lower, const float* __restrict__ norm_w, int H, int dim, int vdim, float eps,
+           float* __restrict__ state, AT* __restrict__ out, int ldo) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  float* S = reinterpret_cast<float*>(hy_smem);                // [dim][vdim]
+  float* qs = S + (size_t)dim * vdim;                          // [dim]
+  float* fs = qs + dim;                                        // [dim]
+  float* os = fs + dim;                                        // [vdim]
+  float* red = os + vdim;                                      // 33
+  const int h = blockIdx.x, e = blockIdx.y, tid = threadIdx.x;
+  const int start = b.ent_start[e], cnt = b.ent_start[e + 1] - start, pos0 = b.ent_pos0[e];
+  float* st = state + ((size_t)b.ent_slot[e] * H + h) * dim * vdim;
+  for (int i = tid; i < dim * vdim; i += blockDim.x) S[i] = pos0 > 0 ? st[i] : 0.0f;
+  for (int j = 0; j < cnt; ++j) {
+    const size_t t = (size_t)(start + j);
+    __syncthreads();
+    for (int k = tid; k < dim; k += blockDim.x) {
+      qs[k] = silu_f(to_f(in[t * ld + col_q + h * dim + k]));
+      const float lo = lower[h * dim + k];
+      fs[k] = fmaf(1.0f - lo, sigmoid_f(to_f(in[t * ld + col_f + h * dim + k]) + f_bias[h * dim + k]), lo);
+    }
+    __syncthreads();
+    float o2 = 0.0f;
+    for (int c = tid; c < vdim; c += blockDim.x) {
+      const float v = to_f(in[t * ld + col_v + h * vdim + c]);
+      float o = 0.0f;
+      for (int i = 0; i < dim; ++i) {
+        const float s = fmaf(fs[i], S[(size_t)i * vdim + c], (1.0f - fs[i]) * v);
+        S[(size_t)i * vdim + c] = s;
+        o = fmaf(s, qs[i], o);
+      }
+      os[c] = o;
+      o2 = fmaf(o, o, o2);
+    }
+    o2 = block_sum(o2, red);
+    const float inv = 1.0f / sqrtf(o2 / (float)vdim + eps);
+    for (int c = tid; c < vdim; c += blockDim.x) out[t * ldo + h * vdim + c] = from_f<AT>(os[c] * inv * norm_w[c]);
+  }
+  __syncthreads();
+  for (int i = tid; i < dim * vdim; i += blockDim.x) st[i] = S[i];
+}
+
+}  // namespace hy

@@ -1,5 +1,5 @@
-"""HybridModelRunner — the per-rank operator of layered hybrid decoders (attention with a sink beside a selective scan,
-gated delta rule layers).  Same place in the engine as ModelRunner (`call("run", ...)`), but the unit of work is a
+"""HybridModelRunner — the per-rank operator of layered hybrid decoders (attention layers over a paged cache, recurrent
+layers over state slots).  Same place in the engine as ModelRunner (`call("run", ...)`), but the unit of work is a
 *portion*: the next tokens of a live request, a slice of its prompt or one decoded token.  One step runs all portions of
 a batch together through libjf_hybrid.so against the paged key cache (pages from the scheduler's BlockManager) and the
 request's recurrent-state slot (StateSlotManager)."""
@@ -45,7 +45,7 @@ class HybridModelRunner:
     @staticmethod
     def _size_cache(hc, config: Config) -> int:
         """Pages for max_num_seqs requests of max_model_len tokens, capped by a share of the device memory."""
-        per_page = sum(2 * s.a_kv_heads * s.a_dim for s in hc.layers if s.mixer == 0) * config.kvcache_block_size
+        per_page = sum(2 * s.cache_elems_per_token() for s in hc.layers) * config.kvcache_block_size
         want = config.max_num_seqs * (-(-config.max_model_len // config.kvcache_block_size) + 1)
         cap = int(64e9 * config.gpu_memory_utilization // max(per_page, 1))
         return int(max(4, min(want, cap, 65536)))

@@ -1,6 +1,13 @@
-"""Configuration of layered hybrid decoders (architecture "Kinetar"): a list of layers over one residual stream, each a
-mixer beside a feed-forward that share one norm.  Mixers: "parallel" (softmax attention with a sink whose values are its
-keys, beside a selective scan) and "channel_delta" (gated delta rule with a decay per key channel).
+"""Configuration of layered hybrid decoders: a list of layers over one residual stream.
+
+Architecture "Kinetar": each layer is a mixer beside a feed-forward that share one RMS norm.  Mixers: "parallel" (softmax
+attention with a sink whose values are its keys, beside a selective scan) and "channel_delta" (gated delta rule with a
+decay per key channel); squared-ReLU feed-forward; sinusoidal positions.
+
+Architecture "Famepel": each layer is norm - mixer - norm, then norm - feed-forward - norm, with element-wise tanh norms
+and a per-channel layer scale on each sublayer.  Mixers: "mamba2" (state-space recurrence with one decay per head),
+"latent_attention" (attention over a shared low-rank latent with a rotated key part and a sink; a layer may use an earlier
+layer's cached latent), "hgrn2" (gated linear recurrence); routed gated experts; positions only through the rotation.
 
 Every size and every constant that can differ between models is read from config.json; sizes that only the tensors know
 (the inner sizes of the two-step decay and gate projections) are read from the checkpoint's tensor shapes."""
@@ -14,8 +21,11 @@ from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 
-MIX_ATTN_SCAN, MIX_DELTA = 0, 1
-FF_NONE, FF_RELU2 = 0, 1
+MIX_ATTN_SCAN, MIX_DELTA, MIX_SSD, MIX_LATENT, MIX_GLR = 0, 1, 2, 3, 4
+FF_NONE, FF_RELU2, FF_ROUTED = 0, 1, 2
+NORM_RMS_OFFSET, NORM_TANH = 0, 1
+BLOCK_PARALLEL, BLOCK_SANDWICH = 0, 1
+POS_SINUSOID, POS_NONE = 0, 1
 _ST_DTYPES = {"BF16": (0, 2), "F32": (1, 4), "F16": (2, 2), "I32": (3, 4)}
 
 
@@ -47,6 +57,89 @@ class LayerSpec:
     d_low_g: int = 0
     ff_kind: int = FF_NONE
     ff: int = 0
+    # state-space recurrence with one decay per head
+    m_heads: int = 0
+    m_vdim: int = 0
+    m_state: int = 0
+    m_groups: int = 1
+    m_conv: int = 1
+    m_norm_groups: int = 1
+    # attention over a shared latent
+    l_heads: int = 0
+    l_dim: int = 0
+    l_rot_dim: int = 0
+    l_vdim: int = 0
+    l_kv_rank: int = 0
+    l_q_rank: int = 0
+    l_kv_from: int = -1
+    l_scale: float = 1.0
+    r_dims: int = 0
+    r_base: float = 10000.0
+    r_factor: float = 0.0
+    r_original: float = 0.0
+    r_fast: float = 0.0
+    r_slow: float = 0.0
+    # gated linear recurrence
+    g_heads: int = 0
+    g_dim: int = 0
+    g_vdim: int = 0
+    # routed experts
+    x_experts: int = 0
+    x_top: int = 0
+    x_groups: int = 1
+    x_keep: int = 1
+    x_scale: float = 1.0
+
+    def cache_elems_per_token(self) -> int:
+        """Elements this layer keeps in the paged cache for every token of a request."""
+        if self.mixer == MIX_ATTN_SCAN:
+            return self.a_kv_heads * self.a_dim
+        if self.mixer == MIX_LATENT and self.l_kv_from < 0:
+            return self.l_kv_rank + self.l_rot_dim
+        return 0
+
+
+def _ssd_spec(m: dict) -> LayerSpec:
+    heads, groups = int(m["heads"]), int(m["groups"])
+    if groups <= 0 or heads % groups:
+        raise ValueError("mamba2: heads must be a multiple of groups")
+    if (heads * int(m["vdim"])) % int(m["norm_groups"]):
+        raise ValueError("mamba2: heads * vdim must be a multiple of norm_groups")
+    return LayerSpec(MIX_SSD, m_heads=heads, m_vdim=int(m["vdim"]), m_state=int(m["state"]), m_groups=groups,
+                     m_conv=int(m["conv"]), m_norm_groups=int(m["norm_groups"]))
+
+
+def _latent_spec(m: dict, i: int, done: List[LayerSpec]) -> LayerSpec:
+    rot = m["rot"]
+    sc = rot.get("scaling") or None
+    spec = LayerSpec(MIX_LATENT, l_heads=int(m["heads"]), l_dim=int(m["dim"]), l_rot_dim=int(m["rot_dim"]),
+                     l_vdim=int(m["vdim"]), l_kv_rank=int(m["kv_rank"]), l_q_rank=int(m["q_rank"]),
+                     l_kv_from=-1 if m.get("kv_from") is None else int(m["kv_from"]), l_scale=float(m["scale"]),
+                     r_dims=int(rot["dims"]), r_base=float(rot["base"]))
+    if sc:
+        spec.r_factor, spec.r_original = float(sc["factor"]), float(sc["original"])
+        spec.r_fast, spec.r_slow = float(sc["fast"]), float(sc["slow"])
+    if spec.r_dims % 2 or spec.r_dims > spec.l_rot_dim:
+        raise ValueError("latent_attention: rot.dims must be even and at most rot_dim")
+    j = spec.l_kv_from
+    if j >= 0:
+        if j >= i or done[j].mixer != MIX_LATENT or done[j].l_kv_from >= 0:
+            raise ValueError(f"layer {i}: kv_from must name an earlier latent_attention layer with a down-projection of its own")
+        if (done[j].l_kv_rank, done[j].l_rot_dim) != (spec.l_kv_rank, spec.l_rot_dim):
+            raise ValueError(f"layer {i}: kv_rank and rot_dim must equal those of layer {j}")
+    return spec
+
+
+def _routed_ff(spec: LayerSpec, mlp: dict) -> None:
+    r = mlp["router"]
+    spec.ff_kind, spec.ff = FF_ROUTED, int(mlp["expert"]["ff"])
+    spec.x_experts, spec.x_top, spec.x_scale = int(r["experts"]), int(r["top"]), float(r["scale"])
+    g = r.get("groups") or {"count": 1, "keep": 1}
+    spec.x_groups, spec.x_keep = int(g["count"]), int(g["keep"])
+    if spec.x_groups <= 0 or spec.x_experts % spec.x_groups or not 1 <= spec.x_keep <= spec.x_groups:
+        raise ValueError("routed feed-forward: experts must split into groups.count equal groups, 1 <= keep <= count")
+    if not 1 <= spec.x_top <= spec.x_keep * (spec.x_experts // spec.x_groups):
+        raise ValueError("routed feed-forward: top exceeds the experts a token may choose from")
 
 
 @dataclass
@@ -58,8 +151,11 @@ class HybridConfig:
     logit_scale: float
     norm_eps: float
     layers: List[LayerSpec] = field(default_factory=list)
+    norm_kind: int = NORM_RMS_OFFSET
+    block_kind: int = BLOCK_PARALLEL
+    pos_kind: int = POS_SINUSOID
     # what the engine's configuration reads from a model description
-    max_position_embeddings: int = 1 << 30          # positions enter through a sinusoid: no table to run out of
+    max_position_embeddings: int = 1 << 30          # positions enter through a sinusoid or a rotation: no table to run out of
     is_hybrid: bool = True
 
     @property
@@ -69,6 +165,8 @@ class HybridConfig:
     @classmethod
     def from_dict(cls, cfg: dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None) -> "HybridConfig":
         """cfg: the parsed config.json; shapes: tensor name -> shape (needed by channel_delta layers)."""
+        if cfg.get("architecture") == "Famepel":
+            return cls._famepel(cfg)
         layers = []
         for i, lc in enumerate(cfg["layers"]):
             m = lc["mixer"]
@@ -98,6 +196,29 @@ class HybridConfig:
         return cls(architecture=cfg["architecture"], width=int(cfg["width"]), vocab=int(cfg["vocab"]),
                    emb_scale=float(cfg["embedding"]["scale"]), logit_scale=float(cfg["logit_scale"]),
                    norm_eps=float(cfg["norm"]["eps"]), layers=layers)
+
+    @classmethod
+    def _famepel(cls, cfg: dict) -> "HybridConfig":
+        layers: List[LayerSpec] = []
+        for i, lc in enumerate(cfg["layers"]):
+            kind, m = lc["type"], lc["mixer"]
+            if kind == "mamba2":
+                spec = _ssd_spec(m)
+            elif kind == "latent_attention":
+                spec = _latent_spec(m, i, layers)
+            elif kind == "hgrn2":
+                spec = LayerSpec(MIX_GLR, g_heads=int(m["heads"]), g_dim=int(m["dim"]), g_vdim=int(m["vdim"]))
+            else:
+                raise NotImplementedError(f"layer type {kind!r}")
+            mlp = lc.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") != "moe":
+                    raise NotImplementedError(f"feed-forward kind {mlp.get('kind')!r}")
+                _routed_ff(spec, mlp)
+            layers.append(spec)
+        return cls(architecture="Famepel", width=int(cfg["width"]), vocab=int(cfg["vocab"]),
+                   emb_scale=float(cfg["embedding"]["scale"]), logit_scale=1.0, norm_eps=float(cfg["norm"]["eps"]),
+                   layers=layers, norm_kind=NORM_TANH, block_kind=BLOCK_SANDWICH, pos_kind=POS_NONE)
 
     @classmethod
     def from_dir(cls, path: str) -> "HybridConfig":

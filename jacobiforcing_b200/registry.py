@@ -39,6 +39,7 @@ FAMILIES: Dict[str, ModelFamily] = {
     "Qwen2ForCausalLM": ModelFamily("qwen2", False, _qwen2_config, _qwen2_runner),
     "Qwen3ForCausalLM": ModelFamily("qwen2", False, _qwen2_config, _qwen2_runner),
     "Kinetar": ModelFamily("hybrid", True, _hybrid_config, _hybrid_runner),
+    "Famepel": ModelFamily("hybrid", True, _hybrid_config, _hybrid_runner),
 }
 
 
