@@ -480,6 +480,32 @@ def run_compare_hybrid(args):
                       "peaks": peaks, "clocks": clocks, "results": res}))
 
 
+def run_compare_famepel(args):
+    """Option --compare-famepel: Famepel (recurrence / gated recurrence / latent attention layers, routed experts) beside
+    the closest existing model, the Kinetar hybrid decoder, at equal width, depth and active feed-forward size; device
+    times from CUDA events, three warm-up passes, weights + activations larger than L2."""
+    import __graft_entry__ as g
+    g.build()
+    from jacobiforcing_b200 import hybrid_bench as hb
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp = json.load(f)
+        peaks = {"hbm_gbs": float(mp["hbm_gbs"]), "bf16_tflops": float(mp["bf16_tflops"]), "source": "measured"}
+    except Exception:
+        peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    mon = ClockSampler(0)
+    mon.start()
+    res = []
+    for size in args.compare_famepel.split(","):
+        row = {"size": size}
+        row["famepel"] = hb.run_hybrid(size, args.hybrid_prompt, args.hybrid_decode_steps, [1, 8], peaks, design="Famepel")
+        row["kinetar"] = hb.run_hybrid(size, args.hybrid_prompt, args.hybrid_decode_steps, [1, 8], peaks)
+        res.append(row)
+    clocks = mon.stop()
+    print(json.dumps({"metric": "famepel_vs_kinetar_throughput", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+                      "peaks": peaks, "clocks": clocks, "results": res}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -507,11 +533,17 @@ def main():
     ap.add_argument("--compare-hybrid", default="", metavar="SIZES",
                     help="instead of the headline workload: prefill / decode throughput of the layered hybrid decoder "
                          "(Kinetar) beside Qwen2 at equal size, e.g. w1024,w2048,w4096 (one JSON line)")
+    ap.add_argument("--compare-famepel", default="", metavar="SIZES",
+                    help="instead of the headline workload: prefill / decode throughput of Famepel beside the Kinetar hybrid "
+                         "decoder at equal size, e.g. w1024,w2048 (one JSON line)")
     ap.add_argument("--hybrid-prompt", type=int, default=4096)
     ap.add_argument("--hybrid-decode-steps", type=int, default=35)
     args = ap.parse_args()
     if args.compare_hybrid:
         run_compare_hybrid(args)
+        return
+    if args.compare_famepel:
+        run_compare_famepel(args)
         return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3                                  # timing rule: at least three warm-up steps

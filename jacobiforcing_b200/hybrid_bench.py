@@ -1,7 +1,8 @@
-"""Throughput of the layered hybrid decoder (Kinetar) beside the Qwen2 engine at equal width / depth / feed-forward size:
-prefill tokens/s, decode tokens/s, device time per kernel group of the hybrid decoder with its distance from the
-roofline (tensor peak for prefill products, HBM bandwidth for decode).  Random weights, synthetic tokens.  Used by
-`bench.py --compare-hybrid`."""
+"""Throughput of the layered hybrid decoders beside the closest existing model at equal size: prefill tokens/s, decode
+tokens/s, device time per kernel group with its distance from the roofline (tensor peak for prefill products, HBM
+bandwidth for decode).  Random weights, synthetic tokens.  `bench.py --compare-hybrid`: Kinetar beside the Qwen2 engine at
+equal width / depth / feed-forward size.  `bench.py --compare-famepel`: Famepel beside Kinetar at equal width / depth and
+equal ACTIVE feed-forward size per token (top x expert size = the dense size)."""
 from __future__ import annotations
 
 import time
@@ -69,8 +70,111 @@ def hybrid_weights(desc: dict, seed: int, low: int = 64) -> Dict[str, np.ndarray
     return w
 
 
+def famepel_description(sz: dict) -> dict:
+    """Layers in the order recurrence, gated recurrence, recurrence, latent attention (the last attention layer borrows the
+    first one's cache when there are two), sizes in the proportions of published models of each kind: recurrence inner =
+    2 width in heads of 64 with a state of 128; latent attention with a key/value rank of 512 + 64 rotated, query rank
+    3 width / 4, heads of 128; routed experts of ff / top each, `top` of 8 x top experts per token."""
+    W, top = sz["width"], sz.get("top", 4)
+    ff = sz["ff"] // top
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": 8 * top, "top": top, "scale": 2.5,
+                                                             "groups": {"count": 4, "keep": 2}}}
+    ssd = {"type": "mamba2", "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8},
+           "mlp": mlp}
+    glr = {"type": "hgrn2", "mixer": {"heads": W // 128, "dim": 128, "vdim": 128}, "mlp": mlp}
+
+    def lat(kv_from=None):
+        m = {"heads": sz["heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": sz.get("kv_rank", 512), "q_rank": 3 * W // 4,
+             "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64,
+                                           "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+    order = ["ssd", "glr", "ssd", "lat"]
+    layers, first_lat = [], None
+    for i in range(sz["layers"]):
+        k = order[i % 4]
+        if k == "lat":
+            layers.append(lat(first_lat))
+            first_lat = i if first_lat is None else first_lat
+        else:
+            layers.append(ssd if k == "ssd" else glr)
+    return {"architecture": "Famepel", "embedding": {"scale": 1.0}, "layers": layers, "norm": {"eps": 1e-6},
+            "vocab": sz["vocab"], "width": W}
+
+
+def famepel_weights(desc: dict, seed: int) -> Dict[str, np.ndarray]:
+    rng = np.random.default_rng(seed)
+    W, V = desc["width"], desc["vocab"]
+
+    def lin(n, k):
+        return (rng.standard_normal((n, k), dtype=np.float32) / np.sqrt(k)).astype(np.float32)
+
+    def vec(n, s=0.1, b=0.0):
+        return (rng.standard_normal(n, dtype=np.float32) * s + b).astype(np.float32)
+    w = {"embed": lin(V, W) * 4.0, "head": lin(V, W)}
+
+    def norm(name):
+        w[name], w[name + ".b"], w[name + ".alpha"] = vec(W, 0.1, 1.0), vec(W), np.float32(0.7).reshape(())
+    norm("final.norm")
+    for i, lc in enumerate(desc["layers"]):
+        p, m, M = f"l{i}.", lc["mixer"], f"l{i}.mix."
+        for n in ("norm1", "norm1b", "norm2", "norm2b"):
+            norm(p + n)
+        w[p + "ls1"], w[p + "ls2"] = vec(W, 0.1, 0.7), vec(W, 0.1, 0.7)
+        if lc["type"] == "mamba2":
+            H, inner, gn = m["heads"], m["heads"] * m["vdim"], m["groups"] * m["state"]
+            w.update({M + "in": lin(2 * inner + 2 * gn + H, W), M + "conv": vec((inner + 2 * gn, m["conv"]), 0.5),
+                      M + "conv.b": vec(inner + 2 * gn), M + "dt_bias": vec(H, 0.5, -1.0),
+                      M + "A_log": np.log(rng.uniform(0.2, 2.0, H)).astype(np.float32), M + "D": vec(H, 0.3, 1.0),
+                      M + "norm": vec(inner, 0.1, 1.0), M + "o": lin(W, inner)})
+        elif lc["type"] == "latent_attention":
+            H, R = m["heads"], m["kv_rank"]
+            w.update({M + "dq": lin(m["q_rank"], W), M + "dq.norm": vec(m["q_rank"], 0.1, 1.0),
+                      M + "uq": lin(H * (m["dim"] + m["rot_dim"]), m["q_rank"]), M + "uk": lin(H * m["dim"], R),
+                      M + "uv": lin(H * m["vdim"], R), M + "sink": vec(H, 1.0), M + "o": lin(W, H * m["vdim"])})
+            if m.get("kv_from") is None:
+                w.update({M + "dkv": lin(R + m["rot_dim"], W), M + "dkv.norm": vec(R, 0.1, 1.0)})
+        else:
+            nq, nv = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            w.update({M + "q": lin(nq, W), M + "f": lin(nq, W), M + "f.b": vec(nq, 0.5), M + "lower": rng.uniform(0, 0.9, nq).astype(np.float32),
+                      M + "v": lin(nv, W), M + "norm": vec(m["vdim"], 0.1, 1.0), M + "o": lin(W, nv)})
+        ff, E = lc["mlp"]["expert"]["ff"], lc["mlp"]["router"]["experts"]
+        w[p + "mlp.router"] = lin(E, W) * 2.0
+        for e in range(E):
+            w[f"{p}mlp.e{e}.gate"], w[f"{p}mlp.e{e}.up"], w[f"{p}mlp.e{e}.down"] = lin(ff, W), lin(ff, W), lin(W, ff)
+    return w
+
+
+def _famepel_costs(desc: dict, hc) -> dict:
+    """Multiply-adds per token per kernel group; for the experts both the work of a token (its `top` experts) and the
+    weights of ALL experts (what a long prefill streams once per step)."""
+    W = desc["width"]
+    per = {"gemm_in": 0, "gemm_out": 0, "small_gemm": 0, "experts": 0, "expert_weights": 0}
+    for s in hc.layers:
+        if s.mixer == 2:
+            inner = s.m_heads * s.m_vdim
+            per["gemm_in"] += (2 * inner + 2 * s.m_groups * s.m_state + s.m_heads) * W
+            per["gemm_out"] += inner * W
+        elif s.mixer == 3:
+            own = s.l_kv_from < 0
+            per["gemm_in"] += (s.l_q_rank + (s.l_kv_rank + s.l_rot_dim if own else 0)) * W
+            per["gemm_out"] += s.l_heads * s.l_vdim * W
+            per["small_gemm"] += s.l_heads * ((s.l_dim + s.l_rot_dim) * s.l_q_rank + s.l_dim * s.l_kv_rank + s.l_vdim * s.l_kv_rank)
+        else:
+            per["gemm_in"] += (2 * s.g_heads * s.g_dim + s.g_heads * s.g_vdim) * W
+            per["gemm_out"] += s.g_heads * s.g_vdim * W
+        if s.ff_kind == 2:
+            per["experts"] += s.x_top * 3 * s.ff * W
+            per["expert_weights"] += s.x_experts * 3 * s.ff * W
+    per["head"] = desc["vocab"] * W
+    return per
+
+
 def _hybrid_costs(desc: dict, hc) -> dict:
     """Multiply-add FLOPs per token and weight bytes per kernel group (bf16 weights)."""
+    if desc["architecture"] == "Famepel":
+        return _famepel_costs(desc, hc)
     W = desc["width"]
     per = {"gemm_in": 0, "gemm_out": 0, "small_gemm": 0}
     for s in hc.layers:
@@ -90,12 +194,17 @@ def _hybrid_costs(desc: dict, hc) -> dict:
     return per
 
 
-def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], peaks: dict, seed: int = 0) -> dict:
+def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], peaks: dict, seed: int = 0,
+               design: str = "Kinetar") -> dict:
     from .hybrid_config import HybridConfig
     from .hybrid_runtime import HybridRuntime
     sz = SIZES[size]
-    desc = hybrid_description(sz)
-    w = hybrid_weights(desc, seed)
+    if design == "Famepel":
+        desc = famepel_description(sz)
+        w = famepel_weights(desc, seed)
+    else:
+        desc = hybrid_description(sz)
+        w = hybrid_weights(desc, seed)
     hc = HybridConfig.from_dict(desc, {k: v.shape for k, v in w.items()})
     page = 256
     maxb = max(batches)
@@ -130,7 +239,7 @@ def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], pe
     out["prefill"] = {"tokens": prompt, "device_ms": ms, "tokens_per_s": prompt / ms * 1e3, "e2e_tokens_per_s": prompt / wall,
                       "ms_by_group": {k: v / 3 for k, v in prof.items()}}
     tf = {}
-    for g in ("gemm_in", "gemm_out"):
+    for g in ("gemm_in", "gemm_out") + (("experts",) if costs.get("experts") else ()):
         t = prof[g] / 3 * 1e-3
         tf[g] = {"tflops": 2.0 * costs[g] * prompt / t / 1e12, "of_measured_bf16_peak": 2.0 * costs[g] * prompt / t / 1e12 / peaks["bf16_tflops"]}
     out["prefill"]["roofline"] = tf
@@ -156,7 +265,12 @@ def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], pe
         for g in ("gemm_in", "gemm_out", "head"):
             t = prof[g] / n * 1e-3
             roof[g] = {"gb_per_s": 2.0 * costs[g] / t / 1e9, "of_measured_hbm": 2.0 * costs[g] / t / 1e9 / peaks["hbm_gbs"]}
-        wbytes = 2.0 * sum(costs.values())
+        if costs.get("experts"):
+            # a decoded token reads its `top` experts; B tokens at most B times that (they may share experts)
+            t = prof["experts"] / n * 1e-3
+            roof["experts"] = {"gb_per_s_if_no_expert_is_shared": 2.0 * costs["experts"] * B / t / 1e9,
+                               "of_measured_hbm": min(2.0 * costs["experts"] * B, 2.0 * costs["expert_weights"]) / t / 1e9 / peaks["hbm_gbs"]}
+        wbytes = 2.0 * sum(v for k, v in costs.items() if k != "expert_weights")
         out["decode"][f"batch{B}"] = {"ms_per_step": ms / n, "tokens_per_s": B * n / ms * 1e3, "e2e_tokens_per_s": B * n / wall,
                                       "ms_by_group": {k: v / n for k, v in prof.items()}, "roofline": roof,
                                       "weights_over_time_of_measured_hbm": wbytes / (ms / n * 1e-3) / 1e9 / peaks["hbm_gbs"]}
