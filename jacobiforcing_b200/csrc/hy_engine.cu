@@ -635,7 +635,10 @@ extern "C" int hy_finalize(hy_handle h) {
     int maxH = 0, maxG = 0, maxD = 0;
     for (auto& c : h->lc) {
       if (c.mixer == HY_MIX_ATTN_SCAN) { maxH = std::max(maxH, c.a_heads); maxG = std::max(maxG, c.a_kv_heads); maxD = std::max(maxD, c.a_dim); }
-      if (c.mixer == HY_MIX_LATENT) { maxH = std::max(maxH, c.l_heads); maxG = std::max(maxG, 1); maxD = std::max(maxD, c.l_kv_rank + c.l_rot_dim); }
+      if (c.mixer == HY_MIX_LATENT) {
+        maxH = std::max(maxH, c.l_heads); maxG = std::max(maxG, 1);
+        maxD = std::max(maxD, std::max(c.l_kv_rank + c.l_rot_dim, c.l_kv_rank <= 128 ? 128 : c.l_kv_rank <= 256 ? 256 : 512));
+      }
     }
     if (maxH > 0) {
       h->part_rows = std::max<size_t>(T * maxH, 4096);
@@ -741,9 +744,9 @@ GemmOut to_buf(void* out, int ld) { return GemmOut{out, ld, 1 << 30, nullptr, 0,
 
 // Work units of the tensor-core attention for this step and this head layout; returns false when the layout does not fit
 // the kernel (the SIMT kernel serves it then).
-bool attn_units(hy_engine* h, int E, int T, int H, int G) {
+bool attn_units(hy_engine* h, int E, int T, int H, int G, bool any_ratio = false) {
   const int R = H / G;
-  if (R > 64 || 64 % R) return false;
+  if (!any_ratio && (R > 64 || 64 % R)) return false;
   if (h->units_n > 0 && h->units_H == H && h->units_G == G) return true;
   int maxctx = 1;
   for (int e = 0; e < E; ++e) maxctx = std::max(maxctx, h->step_pos0[e] + h->step_start[e + 1] - h->step_start[e]);
@@ -853,6 +856,30 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
           else attn_mma_kernel<128><<<h->units_n, 128, 0, s>>>(HY_ATTN_ARGS);
 #undef HY_ATTN_ARGS
           attn_combine_kernel<WT, float><<<T * H, 64, 0, s>>>(b, h->part_o, h->part_ml, (const WT*)L.sink, nullptr, 0, H, Dk, R,
+                                                              h->units_split, h->units_ns, 1.0f, h->f2, h->ld_f2);
+          h->launches += 2;
+        }
+      }
+      if constexpr (std::is_same<AT, bf16>::value) {
+        // wide cache rows (or a head count the narrow kernel does not tile): eight warps per tile, values split by warp
+        if (!tc && Dk % 8 == 0 && R <= 512 && h->part_o && attn_units(h, E, T, H, 1, true)) {
+          tc = true;
+          const int nt = R <= 128 ? 2 : R <= 256 ? 4 : 8, pstride = nt * 64;
+          const size_t smem = attn_wide_smem(Dk);
+          static bool wide_attr = false;
+          if (!wide_attr) {
+            cudaFuncSetAttribute(attn_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_wide_smem(640));
+            cudaFuncSetAttribute(attn_wide_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_wide_smem(640));
+            cudaFuncSetAttribute(attn_wide_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_wide_smem(640));
+            wide_attr = true;
+          }
+#define HY_WIDE_ARGS b, h->units_d, cv, h->ld_cv, (const bf16*)L.cache, H, Dk, R, c.l_scale, h->units_split, h->units_ns, pstride, \
+          h->part_o, h->part_ml
+          if (nt == 2) attn_wide_kernel<2><<<h->units_n, 256, smem, s>>>(HY_WIDE_ARGS);
+          else if (nt == 4) attn_wide_kernel<4><<<h->units_n, 256, smem, s>>>(HY_WIDE_ARGS);
+          else attn_wide_kernel<8><<<h->units_n, 256, smem, s>>>(HY_WIDE_ARGS);
+#undef HY_WIDE_ARGS
+          attn_combine_kernel<WT, float><<<T * H, 64, 0, s>>>(b, h->part_o, h->part_ml, (const WT*)L.sink, nullptr, 0, H, pstride, R,
                                                               h->units_split, h->units_ns, 1.0f, h->f2, h->ld_f2);
           h->launches += 2;
         }

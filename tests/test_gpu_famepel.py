@@ -138,12 +138,15 @@ def test_marked_key_far_back_is_found(needle_at, decode):
 
 @pytest.mark.parametrize("sizes", [dict(), dict(rank=48, rot_dim=16, dim=16, heads=4, vdim=24, width=64),
                                    dict(rank=96, rot_dim=32, dim=24, heads=8, vdim=16, width=64),
-                                   dict(rank=40, rot_dim=8, dim=16, heads=3, vdim=24, width=64)])
+                                   dict(rank=40, rot_dim=8, dim=16, heads=3, vdim=24, width=64),
+                                   dict(rank=200, rot_dim=24, dim=16, heads=5, vdim=24, width=64),
+                                   dict(rank=512, rot_dim=64, dim=32, heads=16, vdim=16, width=64),
+                                   dict(rank=36, rot_dim=6, dim=16, heads=2, vdim=24, width=64)])
 @pytest.mark.parametrize("needle_at", [0, 62, 63, 64, 255, 256, 300])
 @pytest.mark.parametrize("decode", [False, True])
 def test_marked_key_bfloat16_attention(sizes, needle_at, decode):
-    """Cache rows of 32, 64 and 128 elements take the tensor-core attention (64-key tiles, key splits of 256), the last
-    size (48 elements, three heads) the warp-per-row kernel."""
+    """Cache rows of 32, 64 and 128 elements take the narrow tensor-core attention (64-key tiles, key splits of 256); rows
+    of 48 (three heads), 224 (five heads) and 576 elements the wide one; rows of 42 elements the warp-per-row kernel."""
     cfg, w = needle_model(**sizes)
     n = 330
     toks, without = needle_tokens(n, needle_at)
