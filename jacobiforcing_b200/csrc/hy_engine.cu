@@ -60,6 +60,8 @@ struct LayerW {
   float* g_fb = nullptr; float* g_lower = nullptr; float* g_norm = nullptr;
   // routed experts: router [experts, width], gate/up [experts][2 ff][width], down [experts][width][ff]
   void* w_router = nullptr; void* w_gu = nullptr; void* w_down = nullptr;
+  // the same as swizzled tiles per expert for the tensor-core product: gate/up rows alternate in blocks of 16
+  void* w_gu_t = nullptr; void* w_down_t = nullptr; size_t gu_t_stride = 0, down_t_stride = 0; int gu_rows = 0;
 };
 
 }  // namespace hy
@@ -473,6 +475,34 @@ int finalize_sandwich_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
     if (B.rc != HY_OK) return B.rc;
     L.w_gu = B.up(gu);
     L.w_down = B.up(dn);
+    if (h->m.dtype == HY_DTYPE_BF16 && W % 8 == 0 && ff % 8 == 0) {
+      // per expert: rows [32 b, 32 b + 16) = gate features [16 b, ...), rows [32 b + 16, 32 b + 32) = the up features
+      const int fb = (ff + 15) / 16, rows = fb * 32;
+      std::vector<float> il((size_t)rows * W);
+      std::vector<uint16_t> all, one;
+      for (int e = 0; e < E; ++e) {
+        std::fill(il.begin(), il.end(), 0.0f);
+        const float* g = &gu[(size_t)e * 2 * ff * W];
+        for (int f = 0; f < ff; ++f) {
+          memcpy(&il[((size_t)(f / 16) * 32 + f % 16) * W], g + (size_t)f * W, (size_t)W * 4);
+          memcpy(&il[((size_t)(f / 16) * 32 + 16 + f % 16) * W], g + (size_t)(ff + f) * W, (size_t)W * 4);
+        }
+        pack_tiles(il.data(), rows, W, one);
+        all.insert(all.end(), one.begin(), one.end());
+        L.gu_t_stride = one.size();
+      }
+      L.gu_rows = rows;
+      if (dev_alloc(h, &L.w_gu_t, all.size() * 2, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
+      cudaMemcpy(L.w_gu_t, all.data(), all.size() * 2, cudaMemcpyHostToDevice);
+      all.clear();
+      for (int e = 0; e < E; ++e) {
+        pack_tiles(&dn[(size_t)e * W * ff], W, ff, one);
+        all.insert(all.end(), one.begin(), one.end());
+        L.down_t_stride = one.size();
+      }
+      if (dev_alloc(h, &L.w_down_t, all.size() * 2, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
+      cudaMemcpy(L.w_down_t, all.data(), all.size() * 2, cudaMemcpyHostToDevice);
+    }
     mx.f1 = std::max(mx.f1, E);
     mx.in = std::max(mx.in, c.x_top * ((ff + 7) & ~7));
     mx.f2 = std::max(mx.f2, c.x_top * W);
@@ -655,7 +685,7 @@ extern "C" int hy_finalize(hy_handle h) {
       if (c.ff_kind == HY_FF_ROUTED) { maxE = std::max(maxE, c.x_experts); maxTop = std::max(maxTop, c.x_top); }
     if (maxE > 0) {
       const size_t P = T * (size_t)maxTop;
-      h->x_max_tiles = (int)(P / HY_XT) + maxE + 1;
+      h->x_max_tiles = (int)(P / HY_XT) + maxE + 1;          // enough for tiles of HY_XT rows and of 128 rows
       if (dev_alloc(h, (void**)&h->x_ids, P * 4, &h->bytes_ws)) return HY_ERR_CUDA;
       if (dev_alloc(h, (void**)&h->x_wts, P * 4, &h->bytes_ws)) return HY_ERR_CUDA;
       if (dev_alloc(h, (void**)&h->x_row_tok, P * 4, &h->bytes_ws)) return HY_ERR_CUDA;
@@ -700,10 +730,10 @@ int gemm(hy_engine* h, const TA* A, int lda, const TW* Wt, int ldw, int T, int N
       // 256-row tiles halve the weight traffic per row; 128-row tiles when the wider ones would leave SMs without a CTA
       if (T > 128 && (long long)((N + 127) / 128) * ((T + 255) / 256) >= 148)
         gemm_tc_kernel<TO, 256><<<dim3((N + 127) / 128, (T + 255) / 256), 192, tc_smem_bytes(256), h->stream>>>(
-            A, lda, (const bf16*)tiled, T, N, K, o, h->err_d);
+            A, lda, (const bf16*)tiled, T, N, K, o, h->err_d, TcGroup{});
       else
         gemm_tc_kernel<TO, 128><<<dim3((N + 127) / 128, (T + 127) / 128), 192, tc_smem_bytes(128), h->stream>>>(
-            A, lda, (const bf16*)tiled, T, N, K, o, h->err_d);
+            A, lda, (const bf16*)tiled, T, N, K, o, h->err_d, TcGroup{});
       h->launches++;
       return HY_OK;
     }
@@ -935,6 +965,7 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
     h->launches++;
   }
   const bool few = P <= 32;
+  const bool tc_experts = std::is_same<AT, bf16>::value && L.w_gu_t != nullptr;
   {
     ProfScope ps(h, HY_PROF_ROUTE);
     gemm<AT, WT, float>(h, hb, W, (const WT*)L.w_router, W, T, NE, W, to_buf(h->f1, h->ld_f1));
@@ -942,7 +973,8 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
     route_kernel<<<T, 32, (size_t)(NE + c.x_groups) * 4, s>>>(h->f1, h->ld_f1, rc, h->x_ids, h->x_wts, few ? nullptr : h->x_counts);
     h->launches++;
     if (!few) {
-      route_offsets_kernel<<<1, 32, 0, s>>>(h->x_counts, NE, h->x_offs, h->x_fill, h->x_tile_e, h->x_tile_r0, h->x_meta);
+      route_offsets_kernel<<<1, 32, 0, s>>>(h->x_counts, NE, tc_experts ? 128 : HY_XT, h->x_offs, h->x_fill, h->x_tile_e,
+                                            h->x_tile_r0, h->x_meta);
       route_scatter_kernel<<<(P + 255) / 256, 256, 0, s>>>(P, top, h->x_ids, h->x_offs, h->x_fill, h->x_row_tok, h->x_pair_row);
       h->launches += 2;
     }
@@ -961,6 +993,24 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
           hb, W, h->x_ids, top, 1, (const WT*)L.w_gu, (size_t)2 * ff * W, ff, W, pin, ldh);
       expert_rows_kernel<AT, WT, float, false><<<dim3(std::min((W + 7) / 8, 256), P), 256, (size_t)ff * sizeof(AT), s>>>(
           pin, ldh, h->x_ids, top, 0, (const WT*)L.w_down, (size_t)W * ff, W, ff, ys, W);
+    } else if (tc_experts) {
+      if constexpr (std::is_same<AT, bf16>::value) {
+        static bool attr_set = false;
+        if (!attr_set) {
+          cudaFuncSetAttribute(gemm_tc_kernel<bf16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(128));
+          cudaFuncSetAttribute(gemm_tc_kernel<float, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(128));
+          attr_set = true;
+        }
+        const int tiles = std::min(h->x_max_tiles, P / 128 + NE + 1);
+        const TcGroup g1{h->x_meta, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_row_tok, L.gu_t_stride};
+        const TcGroup g2{h->x_meta, h->x_offs, h->x_tile_e, h->x_tile_r0, nullptr, L.down_t_stride};
+        GemmOut o1{pin, ldh, ff, nullptr, 0, 2, nullptr, 0, 1.0f};
+        gemm_tc_kernel<bf16, 128><<<dim3((L.gu_rows + 127) / 128, tiles), 192, tc_smem_bytes(128), s>>>(
+            hb, W, (const bf16*)L.w_gu_t, P, L.gu_rows, W, o1, h->err_d, g1);
+        GemmOut o2 = to_buf(ys, W);
+        gemm_tc_kernel<float, 128><<<dim3((W + 127) / 128, tiles), 192, tc_smem_bytes(128), s>>>(
+            pin, ldh, (const bf16*)L.w_down_t, P, W, ff, o2, h->err_d, g2);
+      }
     } else {
       const int tiles = std::min(h->x_max_tiles, P / HY_XT + NE + 1);
       expert_gemm_simt_kernel<AT, WT, AT, true><<<dim3((ff + 63) / 64, tiles), 256, 0, s>>>(

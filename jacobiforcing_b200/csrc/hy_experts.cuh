@@ -61,16 +61,18 @@ __global__ void __launch_bounds__(32) route_kernel(const float* __restrict__ log
   for (int k = 0; k < c.top; ++k) wts[(size_t)t * c.top + k] *= f;
 }
 
-// Tiles of HY_XT rows of one expert.  meta: [0] number of tiles; offs [experts + 1]; fill [experts] zeroed here.
+// Tiles of tile_rows rows of one expert (HY_XT for the SIMT product, 128 for the tensor-core product).  meta: [0] number
+// of tiles; offs [experts + 1]; fill [experts] zeroed here.
 constexpr int HY_XT = 64;
-__global__ void route_offsets_kernel(int* __restrict__ counts, int experts, int* __restrict__ offs, int* __restrict__ fill,
-                                     int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ meta) {
+__global__ void route_offsets_kernel(int* __restrict__ counts, int experts, int tile_rows, int* __restrict__ offs,
+                                     int* __restrict__ fill, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                     int* __restrict__ meta) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   int at = 0, nt = 0;
   for (int e = 0; e < experts; ++e) {
     const int n = counts[e];
     offs[e] = at;
-    for (int r = 0; r < n; r += HY_XT) { tile_expert[nt] = e; tile_row0[nt] = at + r; ++nt; }
+    for (int r = 0; r < n; r += tile_rows) { tile_expert[nt] = e; tile_row0[nt] = at + r; ++nt; }
     at += n;
     fill[e] = 0;
     counts[e] = 0;                                             // ready for the next routed layer

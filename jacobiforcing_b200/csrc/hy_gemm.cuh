@@ -36,16 +36,33 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, TcSmem* 
   return false;
 }
 
+// Grouped mode (routed experts): blockIdx.y names a tile of a list; a tile is up to BT consecutive rows [row0, ...) of the
+// expert-sorted order that belong to one expert; its weight tiles start at Wt + expert * w_stride; activation rows are
+// fetched through row_map (NULL: the sorted order itself).  Blocks beyond the list's length leave at once.
+struct TcGroup {
+  const int* meta; const int* offs; const int* tile_expert; const int* tile_row0; const int* row_map; size_t w_stride;
+};
+
+// GemmOut.act2 == 2 (gated pair): the weight rows alternate 16 gate features and the 16 up features that go with them, so
+// lanes l and l + 16 of an epilogue warp hold one pair; silu(gate) * up leaves through out1 at feature n / 2.
 template <typename TO, int BT>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const bf16* __restrict__ X, int lda, const bf16* __restrict__ Wt, int T,
-                                                      int N, int K, GemmOut o, int* err) {
+                                                      int N, int K, GemmOut o, int* err, TcGroup grp) {
   extern __shared__ __align__(16) unsigned char hy_smem[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(hy_smem) + 1023) & ~(uintptr_t)1023);
   constexpr int XTILE = BT * 128;                        // BT rows of 64 bf16
   constexpr int SLOT = TC_WTILE + XTILE;
   TcSmem* sm = reinterpret_cast<TcSmem*>(base + TC_STAGES * SLOT);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * 128, t0 = blockIdx.y * BT;
+  const int n0 = blockIdx.x * 128;
+  int t0 = blockIdx.y * BT;
+  if (grp.meta) {
+    if ((int)blockIdx.y >= grp.meta[0]) return;           // the whole block, before any barrier or tensor memory exists
+    const int e = grp.tile_expert[blockIdx.y];
+    t0 = grp.tile_row0[blockIdx.y];
+    T = grp.offs[e + 1];
+    Wt += (size_t)e * grp.w_stride;
+  }
   const int KT = (K + 63) / 64;
   if (threadIdx.x == 0) {
     for (int i = 0; i < TC_STAGES; ++i) { jf::mbar_init(&sm->full[i], 129); jf::mbar_init(&sm->empty[i], 1); }
@@ -60,6 +77,12 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const bf16* __restrict__ X
 
   if (warp < 4) {
     // ---- activation producers ------------------------------------------------------------------------------------
+    int srow[BT / 16];                                    // source row of each of this thread's loads (-1: beyond the rows)
+#pragma unroll
+    for (int u = 0; u < BT / 16; ++u) {
+      const int t = t0 + ((threadIdx.x + u * 128) >> 3);
+      srow[u] = t < T ? (grp.row_map ? grp.row_map[t] : t) : -1;
+    }
     for (int kt = 0; kt < KT; ++kt) {
       const int s = kt % TC_STAGES;
       unsigned char* xt = base + s * SLOT + TC_WTILE;
@@ -67,11 +90,9 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const bf16* __restrict__ X
       uint4 v[BT / 16];
 #pragma unroll
       for (int u = 0; u < BT / 16; ++u) {
-        const int i = threadIdx.x + u * 128;
-        const int r = i >> 3, c = i & 7;
-        const int t = t0 + r, k = kt * 64 + c * 8;
+        const int k = kt * 64 + ((threadIdx.x + u * 128) & 7) * 8;
         v[u] = make_uint4(0, 0, 0, 0);
-        if (t < T && k < K) v[u] = *reinterpret_cast<const uint4*>(X + (size_t)t * lda + k);
+        if (srow[u] >= 0 && k < K) v[u] = *reinterpret_cast<const uint4*>(X + (size_t)srow[u] * lda + k);
       }
       if (!tc_wait(&sm->empty[s], ((kt / TC_STAGES) & 1) ^ 1, sm, err)) break;     // the slot is free: MMAs that read it retired
 #pragma unroll
@@ -93,6 +114,17 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const bf16* __restrict__ X
         uint32_t v[16];
         jf::tmem_ld16(taddr + c0, v);
         jf::tmem_ld_wait();
+        if (o.act2 == 2) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float mine = __uint_as_float(v[j]);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+            const int f = ((n0 + warp * 32) >> 1) + lane;
+            if (lane < 16 && f < o.split && t0 + c0 + j < T)
+              ((TO*)o.out1)[(size_t)(t0 + c0 + j) * o.ld1 + f] = from_f<TO>(silu_f(mine) * other);
+          }
+          continue;
+        }
         if (n < N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
