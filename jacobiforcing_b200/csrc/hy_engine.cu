@@ -55,11 +55,12 @@ struct LayerW {
   // attention over a shared latent
   float* l_qn = nullptr; float* l_kn = nullptr;
   void* w_uq = nullptr; void* w_uq_t = nullptr; void* w_uk = nullptr; void* w_uvT = nullptr;
+  void* w_ukT = nullptr; void* w_uv = nullptr;            // [H][rank][dim] and [H][vdim][rank]: the few-row kernel's layouts
   Rotation rot{};
   // gated linear recurrence
   float* g_fb = nullptr; float* g_lower = nullptr; float* g_norm = nullptr;
   // routed experts: router [experts, width], gate/up [experts][2 ff][width], down [experts][width][ff]
-  void* w_router = nullptr; void* w_gu = nullptr; void* w_down = nullptr;
+  void* w_router = nullptr; void* w_router_t = nullptr; void* w_gu = nullptr; void* w_down = nullptr;
   // the same as swizzled tiles per expert for the tensor-core product: gate/up rows alternate in blocks of 16
   void* w_gu_t = nullptr; void* w_down_t = nullptr; size_t gu_t_stride = 0, down_t_stride = 0; int gu_rows = 0;
 };
@@ -406,8 +407,16 @@ int finalize_sandwich_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
     if (own) { if (auto t = B.get(d + "dkv.norm", R, -1)) L.l_kn = B.up_f32(t->v); }
     const int nq = H * (c.l_dim + rot);
     if (auto t = B.get(d + "uq", nq, c.l_q_rank)) { L.w_uq = B.up(t->v); L.w_uq_t = B.up_tiled(t->v, nq, c.l_q_rank); }
-    if (auto t = B.get(d + "uk", H * c.l_dim, R)) L.w_uk = B.up(t->v);
+    if (auto t = B.get(d + "uk", H * c.l_dim, R)) {
+      L.w_uk = B.up(t->v);
+      std::vector<float> tr((size_t)H * R * c.l_dim);            // [H][rank][dim]
+      for (int hh = 0; hh < H; ++hh)
+        for (int k = 0; k < c.l_dim; ++k)
+          for (int r = 0; r < R; ++r) tr[((size_t)hh * R + r) * c.l_dim + k] = t->v[((size_t)hh * c.l_dim + k) * R + r];
+      L.w_ukT = B.up(tr);
+    }
     if (auto t = B.get(d + "uv", H * c.l_vdim, R)) {
+      L.w_uv = B.up(t->v);
       std::vector<float> tr((size_t)H * R * c.l_vdim);           // [H][rank][vdim]
       for (int hh = 0; hh < H; ++hh)
         for (int j = 0; j < c.l_vdim; ++j)
@@ -462,7 +471,7 @@ int finalize_sandwich_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
     tanh_norm_load(B, p + "norm2b", W, &L.n2b);
     if (auto t = B.get(p + "ls2", W, -1)) L.ls2 = B.up_f32(t->v);
     const int E = c.x_experts, ff = c.ff;
-    if (auto t = B.get(p + "mlp.router", E, W)) L.w_router = B.up(t->v);
+    if (auto t = B.get(p + "mlp.router", E, W)) { L.w_router = B.up(t->v); L.w_router_t = B.up_tiled(t->v, E, W); }
     std::vector<float> gu, dn;
     gu.reserve((size_t)E * 2 * ff * W);
     dn.reserve((size_t)E * W * ff);
@@ -789,7 +798,7 @@ bool attn_units(hy_engine* h, int E, int T, int H, int G, bool any_ratio = false
   for (int e = 0; e < E; ++e) {
     const int cnt = h->step_start[e + 1] - h->step_start[e], pos0 = h->step_pos0[e], rows = cnt * R;
     for (int g = 0; g < G; ++g)
-      for (int row0 = 0; row0 < rows; row0 += 64) {
+      for (int row0 = (rows - 1) / 64 * 64; row0 >= 0; row0 -= 64) {          // late rows see the most keys: start them first
         const int last_pos = pos0 + std::min(row0 + 63, rows - 1) / R;
         for (int sp = 0; sp * split <= last_pos; ++sp) {
           if (n >= h->units_cap) return false;
@@ -868,10 +877,16 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
     {
       ProfScope ps(h, HY_PROF_SMALL_GEMM);
       gemm<AT, WT, AT>(h, cv, h->ld_cv, (const WT*)L.w_uq, c.l_q_rank, T, H * (dn + rot), c.l_q_rank, to_buf(pin, h->ld_pin), L.w_uq_t);
-      latent_query_kernel<AT, WT><<<dim3((T + HY_LAT_TB - 1) / HY_LAT_TB, H, (R + 127) / 128), 128,
+      const int fold = T > 8 ? 1 : 0;
+      latent_query_kernel<AT, WT><<<dim3((T + HY_LAT_TB - 1) / HY_LAT_TB, H, fold ? (R + 127) / 128 : 1), 128,
                                     (size_t)(HY_LAT_TB * dn + 2 * L.rot.pairs + 2) * 4, s>>>(b, pin, h->ld_pin, (const WT*)L.w_uk, H, dn,
-                                                                                             rot, R, L.rot, cv, h->ld_cv);
+                                                                                             rot, R, fold, L.rot, cv, h->ld_cv);
       h->launches++;
+      if (!fold) {
+        head_rows_kernel<AT, WT, AT><<<(H * R + 7) / 8, 256, 0, s>>>(T, pin, h->ld_pin, dn + rot, (const WT*)L.w_ukT, H, R, dn, cv,
+                                                                     h->ld_cv, Dk);
+        h->launches++;
+      }
     }
     {
       ProfScope ps(h, HY_PROF_ATTN);
@@ -923,6 +938,10 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
     }
     {
       ProfScope ps(h, HY_PROF_SMALL_GEMM);
+      if (T <= 8)
+        head_rows_kernel<float, WT, AT><<<(H * dv + 7) / 8, 256, 0, s>>>(T, h->f2, h->ld_f2, R, (const WT*)L.w_uv, H, dv, R, cat,
+                                                                         h->ld_cat, dv);
+      else
       latent_value_kernel<AT, WT><<<dim3((T + HY_LAT_TB - 1) / HY_LAT_TB, H, (dv + 127) / 128), 128, (size_t)HY_LAT_TB * R * 4, s>>>(
           T, h->f2, h->ld_f2, (const WT*)L.w_uvT, H, R, dv, cat, h->ld_cat);
       h->launches++;
@@ -968,7 +987,7 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
   const bool tc_experts = std::is_same<AT, bf16>::value && L.w_gu_t != nullptr;
   {
     ProfScope ps(h, HY_PROF_ROUTE);
-    gemm<AT, WT, float>(h, hb, W, (const WT*)L.w_router, W, T, NE, W, to_buf(h->f1, h->ld_f1));
+    gemm<AT, WT, float>(h, hb, W, (const WT*)L.w_router, W, T, NE, W, to_buf(h->f1, h->ld_f1), L.w_router_t);
     const RouteCfg rc{NE, top, c.x_groups, c.x_keep, c.x_scale};
     route_kernel<<<T, 32, (size_t)(NE + c.x_groups) * 4, s>>>(h->f1, h->ld_f1, rc, h->x_ids, h->x_wts, few ? nullptr : h->x_counts);
     h->launches++;

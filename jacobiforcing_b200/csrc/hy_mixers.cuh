@@ -172,10 +172,11 @@ __global__ void latent_prep_kernel(Batch b, const float* __restrict__ d, int ldd
 // q [T, ldq] holds heads of [dim | rot]; w_uk [H * dim, rank] row-major (thread r walks a column: coalesced across r).
 // A block serves HY_LAT_TB tokens of one head and 128 output dimensions, so a weight element is read once per 8 tokens.
 constexpr int HY_LAT_TB = 8;
+// fold == 0: only the rotated part is written (a few-row step folds the key up-projection with head_rows_kernel).
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(128) latent_query_kernel(Batch b, const AT* __restrict__ q, int ldq, const WT* __restrict__ w_uk,
-                                                           int H, int dim, int rot, int rank, Rotation r, AT* __restrict__ out,
-                                                           int ldo) {
+                                                           int H, int dim, int rot, int rank, int fold, Rotation r,
+                                                           AT* __restrict__ out, int ldo) {
   extern __shared__ __align__(16) unsigned char hy_smem[];
   float* qs = reinterpret_cast<float*>(hy_smem);              // [TB][dim]
   float* cs = qs + HY_LAT_TB * dim;                           // [2 * pairs] of one token at a time
@@ -186,7 +187,7 @@ __global__ void __launch_bounds__(128) latent_query_kernel(Batch b, const AT* __
   }
   __syncthreads();
   const int c = blockIdx.z * blockDim.x + threadIdx.x;
-  if (c < rank) {
+  if (fold && c < rank) {
     float acc[HY_LAT_TB];
 #pragma unroll
     for (int tt = 0; tt < HY_LAT_TB; ++tt) acc[tt] = 0.0f;
@@ -240,6 +241,48 @@ __global__ void __launch_bounds__(128) latent_value_kernel(int T, const float* _
     for (int tt = 0; tt < HY_LAT_TB; ++tt) acc[tt] = fmaf(os[tt * rank + k], w, acc[tt]);
   }
   for (int tt = 0; tt < nb; ++tt) out[(size_t)(t0 + tt) * ldo + h * vdim + j] = from_f<AT>(acc[tt]);
+}
+
+// Few rows (decode steps): out[t, h, n] = sum_k in[t, h, k] w[h][n][k] for up to 8 rows t.  One warp per (h, n) walks a
+// weight row 16 bytes per lane (both per-head projections around the attention are stored [n][k] for this kernel as well),
+// so the weights stream once at full width instead of one block per head walking them column by column.
+template <typename TI, typename TW, typename TO>
+__global__ void __launch_bounds__(256) head_rows_kernel(int T, const TI* __restrict__ in, int ldi, int in_hs, const TW* __restrict__ w,
+                                                        int H, int N, int K, TO* __restrict__ out, int ldo, int out_hs) {
+  constexpr int VEC = 16 / sizeof(TW);
+  const int lane = threadIdx.x & 31;
+  const int id = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (id >= H * N) return;
+  const int h = id / N, n = id % N;
+  const TW* wr = w + ((size_t)h * N + n) * K;
+  float acc[8];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) acc[t] = 0.0f;
+  if (K % VEC == 0 && (reinterpret_cast<uintptr_t>(wr) & 15) == 0) {
+    for (int k = lane * VEC; k < K; k += 32 * VEC) {
+      const VecN<TW, VEC> wv = *reinterpret_cast<const VecN<TW, VEC>*>(wr + k);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        if (t >= T) break;
+        const TI* ir = in + (size_t)t * ldi + h * in_hs + k;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[t] = fmaf(to_f(ir[j]), to_f(wv.v[j]), acc[t]);
+      }
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      const float wv = to_f(wr[k]);
+#pragma unroll
+      for (int t = 0; t < 8; ++t)
+        if (t < T) acc[t] = fmaf(to_f(in[(size_t)t * ldi + h * in_hs + k]), wv, acc[t]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    if (t >= T) break;
+    const float v = warp_sum(acc[t]);
+    if (lane == 0) out[(size_t)t * ldo + h * out_hs + n] = from_f<TO>(v);
+  }
 }
 
 // ---- gated linear recurrence ------------------------------------------------------------------------------------------------------
