@@ -176,7 +176,7 @@ extern "C" int hy_create(const hy_model_cfg* model, const hy_layer_cfg* layers, 
       if (c.d_conv > HY_MAX_TAPS || c.d_conv < 1) return bad("conv taps must lie in 1..16");
     } else if (c.mixer == HY_MIX_SSD) {
       if (c.m_heads <= 0 || c.m_vdim <= 0 || c.m_groups <= 0 || c.m_heads % c.m_groups) return bad("recurrence heads must be a multiple of its groups");
-      if (c.m_state > 256 || c.m_state <= 0) return bad("recurrence state size must lie in 1..256");
+      if (c.m_state > 512 || c.m_state <= 0) return bad("recurrence state size must lie in 1..512");
       if (c.m_conv > HY_MAX_TAPS || c.m_conv < 1) return bad("conv taps must lie in 1..16");
       if (c.m_norm_groups <= 0 || (c.m_heads * c.m_vdim) % c.m_norm_groups) return bad("the output norm's parts must divide heads * vdim");
     } else if (c.mixer == HY_MIX_LATENT) {
@@ -844,7 +844,7 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
     }
     {
       ProfScope ps(h, HY_PROF_SCAN);
-      const int nper = N <= 32 ? 1 : N <= 64 ? 2 : N <= 128 ? 4 : 8;
+      const int nper = N <= 32 ? 1 : N <= 64 ? 2 : N <= 128 ? 4 : N <= 256 ? 8 : 16;
       int lanes = 1;
       while (lanes * nper < N) lanes <<= 1;
       const int per_block = 128 / lanes, bph = (P + per_block - 1) / per_block;
@@ -855,7 +855,8 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
       if (nper == 1) ssd_scan_kernel<AT, 1><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
       else if (nper == 2) ssd_scan_kernel<AT, 2><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
       else if (nper == 4) ssd_scan_kernel<AT, 4><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
-      else ssd_scan_kernel<AT, 8><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
+      else if (nper == 8) ssd_scan_kernel<AT, 8><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
+      else ssd_scan_kernel<AT, 16><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
 #undef HY_SSD_ARGS
       gated_group_norm_kernel<AT><<<dim3(T, c.m_norm_groups), 128, 0, s>>>(h->f2, h->ld_f2, pin, h->ld_pin, L.m_norm, inner,
                                                                           c.m_norm_groups, eps, cat, h->ld_cat);

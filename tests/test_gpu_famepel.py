@@ -30,13 +30,15 @@ def test_mechanism_alone(which, dtype):
 @pytest.mark.parametrize("kw", [dict(experts=8, top=3, count=4, keep=2), dict(experts=5, top=1, count=1, keep=1),
                                 dict(experts=6, top=2, count=6, keep=3), dict(experts=9, top=4, count=3, keep=3),
                                 dict(experts=40, top=2, count=5, keep=1, ff=9)])
-def test_router_shapes(kw):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_router_shapes(kw, dtype):
     """Groups of two, one group, groups of one expert (a group is worth its single score), every group kept, more experts
-    than a warp; many tokens so that the expert-sorted path runs, few so that the per-pair path runs."""
+    than a warp, an expert size that the tensor-core product does not take; many tokens so that the expert-sorted path
+    runs, few so that the per-pair path runs."""
     cfg = model_config([glr(heads=1, dim=4, vdim=4, mlp=moe(**kw)), ssd(heads=2, vdim=4, state=3, groups=1, norm_groups=1, mlp=moe(**kw))])
     toks = rand_tokens(80, cfg["vocab"], 4)
-    got, want = run(cfg, toks, "float32", cuts=[60, 1, 7, 1])
-    assert close(got, want)
+    got, want = run(cfg, toks, dtype, cuts=[60, 1, 7, 1])
+    assert close(got, want, dtype)
 
 
 # ---- prefill == decode, portions -------------------------------------------------------------------------------------------
@@ -224,7 +226,7 @@ OTHER = [
                   glr(heads=1, dim=1, vdim=1, mlp=None)], width=24, vocab=50),
     # groups == heads, norm parts == channels per part of one, a wide state (lanes hold several entries), many taps,
     # a key size above a warp on the gated recurrence, an odd head count in attention, no rotated part at all
-    model_config([ssd(heads=6, vdim=7, state=150, groups=6, conv=6, norm_groups=42),
+    model_config([ssd(heads=6, vdim=7, state=300, groups=6, conv=6, norm_groups=42),
                   glr(heads=2, dim=40, vdim=70),
                   latent(heads=5, dim=12, rot_dim=0, vdim=9, kv_rank=33, q_rank=17, scaling=None),
                   latent(heads=7, dim=6, rot_dim=0, vdim=5, kv_rank=33, q_rank=8, scaling=None, kv_from=2)],
