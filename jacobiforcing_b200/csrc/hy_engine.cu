@@ -844,19 +844,18 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
     }
     {
       ProfScope ps(h, HY_PROF_SCAN);
-      const int nper = N <= 32 ? 1 : N <= 64 ? 2 : N <= 128 ? 4 : N <= 256 ? 8 : 16;
+      // 4 states per thread up to 16 states, 16 per thread beyond; lanes = the power of two that covers the state size
+      const int nper = N <= 16 ? 4 : 16;
       int lanes = 1;
       while (lanes * nper < N) lanes <<= 1;
       const int per_block = 128 / lanes, bph = (P + per_block - 1) / per_block;
       dim3 grid(H * bph, E);
-      const size_t smem = (size_t)HY_SCAN_TB * (2 * N + per_block + 2) * 4;
 #define HY_SSD_ARGS b, cv, h->ld_cv, inner, inner + GN, pin + 2 * inner + 2 * GN, h->ld_pin, L.m_dt_bias, L.m_A_log, L.m_D, H, P, N, \
-      G, lanes, bph, L.rec_state, h->f2, h->ld_f2
-      if (nper == 1) ssd_scan_kernel<AT, 1><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
-      else if (nper == 2) ssd_scan_kernel<AT, 2><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
-      else if (nper == 4) ssd_scan_kernel<AT, 4><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
-      else if (nper == 8) ssd_scan_kernel<AT, 8><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
-      else ssd_scan_kernel<AT, 16><<<grid, 128, smem, s>>>(HY_SSD_ARGS);
+      G, bph, L.rec_state, h->f2, h->ld_f2
+#define HY_SSD_CASE(NP, LL) if (nper == NP && lanes == LL) ssd_scan_kernel<AT, NP, LL><<<grid, 128, 0, s>>>(HY_SSD_ARGS)
+      HY_SSD_CASE(4, 1); else HY_SSD_CASE(4, 2); else HY_SSD_CASE(4, 4);
+      else HY_SSD_CASE(16, 2); else HY_SSD_CASE(16, 4); else HY_SSD_CASE(16, 8); else HY_SSD_CASE(16, 16); else HY_SSD_CASE(16, 32);
+#undef HY_SSD_CASE
 #undef HY_SSD_ARGS
       gated_group_norm_kernel<AT><<<dim3(T, c.m_norm_groups), 128, 0, s>>>(h->f2, h->ld_f2, pin, h->ld_pin, L.m_norm, inner,
                                                                           c.m_norm_groups, eps, cat, h->ld_cat);

@@ -29,27 +29,30 @@ __device__ __forceinline__ void rotation_row(const Rotation& r, int pos, float* 
 // ---- state-space recurrence, one decay per head ----------------------------------------------------------------------------
 // Per head h (group g = h / (heads / groups)), channel p, state n:
 //   dt = softplus(dt_raw_h + dt_bias_h) ; S[p, n] <- exp(-exp(A_log_h) dt) S[p, n] + dt x_p B_n ; y_p = sum_n S[p, n] C_n + D_h x_p
-// L lanes (a power of two) share a channel, each holding NPER states.  xbc [T, ldx]: x at column 0 (heads * vdim), B at
-// col_b, C at col_c (groups * nstate each), after convolution and activation.  state [slot][heads * vdim][nstate] fp32.
-// y leaves in fp32 (it enters a norm).  Inputs of HY_SCAN_TB tokens are staged per block; a block's channels lie in one head.
-template <typename AT, int NPER>
+// L lanes share a channel, each holding NPER CONSECUTIVE states in registers (state sizes up to NPER * L; B and C are
+// staged zero-padded to that size, so the inner loop has no bounds checks and reads them four at a time).  xbc [T, ldx]:
+// x at column 0 (heads * vdim), B at col_b, C at col_c (groups * nstate each), after convolution and activation.
+// state [slot][heads * vdim][nstate] fp32.  y leaves in fp32 (it enters a norm).  Inputs of HY_SSD_TB tokens (fewer for 256 states and more) are staged per
+// block as fp32; a block's 128 / L channels lie in one head.  Per token a thread spends about 3.5 instructions per state
+// plus a short shuffle tree: measured, the per-token overhead (indices, conversions, bounds, a 5-step tree for 4 states)
+// was four fifths of an earlier one-state-per-lane layout's instructions.
+constexpr int HY_SSD_TB = 32;
+template <typename AT, int NPER, int L>
 __global__ void __launch_bounds__(128) ssd_scan_kernel(Batch b, const AT* __restrict__ xbc, int ldx, int col_b, int col_c,
                                                        const AT* __restrict__ dt_raw, int lddt, const float* __restrict__ dt_bias,
                                                        const float* __restrict__ A_log, const float* __restrict__ D, int heads,
-                                                       int vdim, int nstate, int groups, int L, int blocks_per_head,
+                                                       int vdim, int nstate, int groups, int blocks_per_head,
                                                        float* __restrict__ state, float* __restrict__ y, int ldy) {
-  extern __shared__ __align__(16) unsigned char hy_smem[];
+  constexpr int NP = NPER * L, PB = 128 / L, TB = NP >= 512 ? HY_SSD_TB / 4 : NP >= 256 ? HY_SSD_TB / 2 : HY_SSD_TB;
+  __shared__ __align__(16) float sB[TB * NP];
+  __shared__ __align__(16) float sC[TB * NP];
+  __shared__ float sx[TB * PB];
+  __shared__ float sdt[TB], sdec[TB];
   const int e = blockIdx.y;
-  const int per_block = blockDim.x / L;
-  float* sB = reinterpret_cast<float*>(hy_smem);              // [TB][nstate]
-  float* sC = sB + HY_SCAN_TB * nstate;                       // [TB][nstate]
-  float* sx = sC + HY_SCAN_TB * nstate;                       // [TB][per_block]
-  float* sdt = sx + HY_SCAN_TB * per_block;                   // [TB]
-  float* sdec = sdt + HY_SCAN_TB;                             // [TB]
   const int h = blockIdx.x / blocks_per_head;
-  const int p0 = (blockIdx.x % blocks_per_head) * per_block;
+  const int p0 = (blockIdx.x % blocks_per_head) * PB;
   const int g = h / (heads / groups);
-  const int cl = threadIdx.x / L, sub = threadIdx.x % L;
+  const int cl = threadIdx.x / L, sub = threadIdx.x % L, n0 = sub * NPER;
   const int p = p0 + cl;
   const bool live = p < vdim;
   const int pc = live ? p : vdim - 1;
@@ -57,23 +60,26 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(Batch b, const AT* __rest
   float* st = state + (((size_t)b.ent_slot[e] * heads + h) * vdim + pc) * nstate;
   float S[NPER];
 #pragma unroll
-  for (int i = 0; i < NPER; ++i) {
-    const int n = sub + i * L;
-    S[i] = (n < nstate && pos0 > 0) ? st[n] : 0.0f;
-  }
+  for (int i = 0; i < NPER; ++i) S[i] = (n0 + i < nstate && pos0 > 0) ? st[n0 + i] : 0.0f;
   const float rate = expf(A_log[h]), dd = D[h], bias = dt_bias[h];
-  for (int j0 = 0; j0 < cnt; j0 += HY_SCAN_TB) {
-    const int nb = min(HY_SCAN_TB, cnt - j0);
+  const AT* xb = xbc + col_b + g * nstate;
+  const AT* xc = xbc + col_c + g * nstate;
+  const AT* xx = xbc + h * vdim;
+  float* yp = y + h * vdim + p;
+  for (int j0 = 0; j0 < cnt; j0 += TB) {
+    const int nb = min(TB, cnt - j0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nb * nstate; i += blockDim.x) {
-      const int tt = i / nstate, n = i % nstate;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < nb * NP; i += 128) {
+      const int tt = i / NP, n = i % NP;
       const size_t row = (size_t)(start + j0 + tt) * ldx;
-      sB[tt * nstate + n] = to_f(xbc[row + col_b + g * nstate + n]);
-      sC[tt * nstate + n] = to_f(xbc[row + col_c + g * nstate + n]);
+      const bool ok = n < nstate;
+      sB[i] = ok ? to_f(xb[row + n]) : 0.0f;
+      sC[i] = ok ? to_f(xc[row + n]) : 0.0f;
     }
-    for (int i = threadIdx.x; i < nb * per_block; i += blockDim.x) {
-      const int tt = i / per_block, k = i % per_block;
-      sx[i] = to_f(xbc[(size_t)(start + j0 + tt) * ldx + h * vdim + min(p0 + k, vdim - 1)]);
+    for (int i = threadIdx.x; i < nb * PB; i += 128) {
+      const int tt = i / PB, k = i % PB;
+      sx[i] = to_f(xx[(size_t)(start + j0 + tt) * ldx + min(p0 + k, vdim - 1)]);
     }
     if (threadIdx.x < nb) {
       const float dt = softplus_f(to_f(dt_raw[(size_t)(start + j0 + threadIdx.x) * lddt + h]) + bias);
@@ -81,28 +87,39 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(Batch b, const AT* __rest
       sdec[threadIdx.x] = expf(-rate * dt);
     }
     __syncthreads();
-    for (int tt = 0; tt < nb; ++tt) {
-      const float dt = sdt[tt], dec = sdec[tt], xv = sx[tt * per_block + cl];
-      const float dx = dt * xv;
-      float acc = 0.0f;
+    float* yr = yp + (size_t)(start + j0) * ldy;
+    for (int tt = 0; tt < nb; ++tt, yr += ldy) {
+      const float dec = sdec[tt], xv = sx[tt * PB + cl];
+      const float dx = sdt[tt] * xv;
+      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+      if constexpr (NPER % 4 == 0) {
+        const float4* b4 = reinterpret_cast<const float4*>(sB + tt * NP + n0);
+        const float4* c4 = reinterpret_cast<const float4*>(sC + tt * NP + n0);
 #pragma unroll
-      for (int i = 0; i < NPER; ++i) {
-        const int n = sub + i * L;
-        if (n < nstate) {
-          S[i] = fmaf(dec, S[i], dx * sB[tt * nstate + n]);
-          acc = fmaf(S[i], sC[tt * nstate + n], acc);
+        for (int i = 0; i < NPER / 4; ++i) {
+          const float4 bv = b4[i], cv = c4[i];
+          S[4 * i] = fmaf(dec, S[4 * i], dx * bv.x);         a0 = fmaf(S[4 * i], cv.x, a0);
+          S[4 * i + 1] = fmaf(dec, S[4 * i + 1], dx * bv.y); a1 = fmaf(S[4 * i + 1], cv.y, a1);
+          S[4 * i + 2] = fmaf(dec, S[4 * i + 2], dx * bv.z); a2 = fmaf(S[4 * i + 2], cv.z, a2);
+          S[4 * i + 3] = fmaf(dec, S[4 * i + 3], dx * bv.w); a3 = fmaf(S[4 * i + 3], cv.w, a3);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+          S[i] = fmaf(dec, S[i], dx * sB[tt * NP + n0 + i]);
+          a0 = fmaf(S[i], sC[tt * NP + n0 + i], a0);
         }
       }
+      float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
       for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (live && sub == 0) y[(size_t)(start + j0 + tt) * ldy + h * vdim + p] = fmaf(dd, xv, acc);
+      if (live && sub == 0) *yr = fmaf(dd, xv, acc);
     }
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < NPER; ++i) {
-      const int n = sub + i * L;
-      if (n < nstate) st[n] = S[i];
-    }
+    for (int i = 0; i < NPER; ++i)
+      if (n0 + i < nstate) st[n0 + i] = S[i];
   }
 }
 
