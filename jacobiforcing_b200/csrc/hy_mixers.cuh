@@ -66,9 +66,48 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(Batch b, const AT* __rest
   const AT* xc = xbc + col_c + g * nstate;
   const AT* xx = xbc + h * vdim;
   float* yp = y + h * vdim + p;
+  // long entries: the raw inputs of the NEXT batch of tokens are fetched into registers before the current batch runs
+  constexpr int UB = TB * NP / 128, UX = (TB * PB + 127) / 128;
+  const bool ahead = cnt > TB;
+  AT rb[UB], rc[UB], rx[UX], rdt = from_f<AT>(0.0f);
+  auto fetch = [&](int j0, int nb) {
+#pragma unroll
+    for (int u = 0; u < UB; ++u) {
+      const int i = threadIdx.x + u * 128, tt = i / NP, n = i % NP;
+      const bool ok = tt < nb && n < nstate;
+      const size_t row = (size_t)(start + j0 + tt) * ldx;
+      rb[u] = ok ? xb[row + n] : from_f<AT>(0.0f);
+      rc[u] = ok ? xc[row + n] : from_f<AT>(0.0f);
+    }
+#pragma unroll
+    for (int u = 0; u < UX; ++u) {
+      const int i = threadIdx.x + u * 128, tt = i / PB, k = i % PB;
+      rx[u] = tt < nb ? xx[(size_t)(start + j0 + tt) * ldx + min(p0 + k, vdim - 1)] : from_f<AT>(0.0f);
+    }
+    if (threadIdx.x < nb) rdt = dt_raw[(size_t)(start + j0 + threadIdx.x) * lddt + h];
+  };
+  if (ahead) fetch(0, min(TB, cnt));
   for (int j0 = 0; j0 < cnt; j0 += TB) {
     const int nb = min(TB, cnt - j0);
     __syncthreads();
+    if (ahead) {
+#pragma unroll
+      for (int u = 0; u < UB; ++u) {
+        const int i = threadIdx.x + u * 128;
+        sB[i] = to_f(rb[u]);
+        sC[i] = to_f(rc[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < UX; ++u) {
+        const int i = threadIdx.x + u * 128;
+        if (i < TB * PB) sx[i] = to_f(rx[u]);
+      }
+      if (threadIdx.x < nb) {
+        const float dt = softplus_f(to_f(rdt) + bias);
+        sdt[threadIdx.x] = dt;
+        sdec[threadIdx.x] = expf(-rate * dt);
+      }
+    } else {
 #pragma unroll 4
     for (int i = threadIdx.x; i < nb * NP; i += 128) {
       const int tt = i / NP, n = i % NP;
@@ -86,7 +125,9 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(Batch b, const AT* __rest
       sdt[threadIdx.x] = dt;
       sdec[threadIdx.x] = expf(-rate * dt);
     }
+    }
     __syncthreads();
+    if (ahead && j0 + TB < cnt) fetch(j0 + TB, min(TB, cnt - j0 - TB));
     float* yr = yp + (size_t)(start + j0) * ldy;
     for (int tt = 0; tt < nb; ++tt, yr += ldy) {
       const float dec = sdec[tt], xv = sx[tt * PB + cl];
@@ -309,51 +350,93 @@ __global__ void __launch_bounds__(256) head_rows_kernel(int T, const TI* __restr
 // Thread j keeps column j of S in registers (key size <= DR); inputs of HY_GLR_TB tokens are staged by the block, the
 // output norms of the batch are made by one warp per token.
 constexpr int HY_GLR_TB = 16;
+// With 128 threads or more, the raw inputs of the NEXT 16 tokens are fetched into registers before the current 16 run and
+// are activated into shared memory afterwards: one block per head leaves nothing else on its SM to hide the loads behind
+// (measured: the waits for staged loads were the largest stall of the kernel).
 template <typename AT, int DR>
 __global__ void __launch_bounds__(DR > 64 ? 256 : 512)
 glr_reg_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_f, int col_v, const float* __restrict__ f_bias,
                const float* __restrict__ lower, const float* __restrict__ norm_w, int H, int dim, int vdim, float eps,
                float* __restrict__ state, AT* __restrict__ out, int ldo) {
   extern __shared__ __align__(16) unsigned char hy_smem[];
+  constexpr int TB = HY_GLR_TB, UQ = TB * DR / 128;            // q / f elements per thread and batch when nt >= 128
   const int nt = blockDim.x, nwarps = nt >> 5;
   float* sq = reinterpret_cast<float*>(hy_smem);               // [TB][DR] activated queries
-  float* sf = sq + HY_GLR_TB * DR;                             // [TB][DR] forget gates
-  float* sv = sf + HY_GLR_TB * DR;                             // [TB][nt] values
-  float* so = sv + HY_GLR_TB * nt;                             // [TB][nt] raw read-outs
+  float* sf = sq + TB * DR;                                    // [TB][DR] forget gates
+  float* sv = sf + TB * DR;                                    // [TB][nt] values
+  float* so = sv + TB * nt;                                    // [TB][nt] raw read-outs
   const int h = blockIdx.x, e = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int start = b.ent_start[e], cnt = b.ent_start[e + 1] - start, pos0 = b.ent_pos0[e];
   float* st = state + ((size_t)b.ent_slot[e] * H + h) * dim * vdim;
   const bool col = tid < vdim;
+  const bool ahead = nt >= 128 && cnt > TB;                   // short entries (decode steps) stage directly
   float S[DR];
 #pragma unroll
   for (int i = 0; i < DR; ++i) S[i] = (col && i < dim && pos0 > 0) ? st[(size_t)i * vdim + tid] : 0.0f;
-  for (int j0 = 0; j0 < cnt; j0 += HY_GLR_TB) {
-    const int nb = min(HY_GLR_TB, cnt - j0);
-    __syncthreads();
-    for (int i = tid; i < nb * DR; i += nt) {
-      const int tt = i / DR, k = i % DR;
-      const size_t t = (size_t)(start + j0 + tt);
-      const bool ok = k < dim;
-      sq[i] = ok ? silu_f(to_f(in[t * ld + col_q + h * dim + k])) : 0.0f;
-      const float lo = ok ? lower[h * dim + k] : 0.0f;
-      sf[i] = ok ? fmaf(1.0f - lo, sigmoid_f(to_f(in[t * ld + col_f + h * dim + k]) + f_bias[h * dim + k]), lo) : 1.0f;
+  AT rq[UQ], rf[UQ], rv[TB];
+  const AT* inq = in + col_q + h * dim;
+  const AT* inf = in + col_f + h * dim;
+  const AT* inv = in + col_v + h * vdim + (col ? tid : 0);
+  auto fetch = [&](int j0, int nb) {
+#pragma unroll
+    for (int u = 0; u < UQ; ++u) {
+      const int i = tid + u * nt, tt = i / DR, k = i % DR;
+      const bool ok = i < nb * DR && k < dim;
+      const size_t row = (size_t)(start + j0 + tt) * ld;
+      rq[u] = ok ? inq[row + k] : from_f<AT>(0.0f);
+      rf[u] = ok ? inf[row + k] : from_f<AT>(0.0f);
     }
-    for (int i = tid; i < nb * nt; i += nt) {
-      const int tt = i / nt, k = i % nt;
-      sv[i] = k < vdim ? to_f(in[(size_t)(start + j0 + tt) * ld + col_v + h * vdim + k]) : 0.0f;
+#pragma unroll
+    for (int u = 0; u < TB; ++u) rv[u] = (u < nb && col) ? inv[(size_t)(start + j0 + u) * ld] : from_f<AT>(0.0f);
+  };
+  auto activate = [&](int nb) {
+#pragma unroll
+    for (int u = 0; u < UQ; ++u) {
+      const int i = tid + u * nt, k = i % DR;
+      if (i < nb * DR) {
+        const bool ok = k < dim;
+        const float lo = ok ? lower[h * dim + k] : 0.0f;
+        sq[i] = ok ? silu_f(to_f(rq[u])) : 0.0f;
+        sf[i] = ok ? fmaf(1.0f - lo, sigmoid_f(to_f(rf[u]) + f_bias[h * dim + k]), lo) : 1.0f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < TB; ++u)
+      if (u < nb) sv[u * nt + tid] = to_f(rv[u]);
+  };
+  if (ahead) fetch(0, min(TB, cnt));
+  for (int j0 = 0; j0 < cnt; j0 += TB) {
+    const int nb = min(TB, cnt - j0);
+    __syncthreads();
+    if (ahead) {
+      activate(nb);
+    } else {
+      for (int i = tid; i < nb * DR; i += nt) {
+        const int tt = i / DR, k = i % DR;
+        const size_t t = (size_t)(start + j0 + tt);
+        const bool ok = k < dim;
+        sq[i] = ok ? silu_f(to_f(in[t * ld + col_q + h * dim + k])) : 0.0f;
+        const float lo = ok ? lower[h * dim + k] : 0.0f;
+        sf[i] = ok ? fmaf(1.0f - lo, sigmoid_f(to_f(in[t * ld + col_f + h * dim + k]) + f_bias[h * dim + k]), lo) : 1.0f;
+      }
+      for (int i = tid; i < nb * nt; i += nt) {
+        const int tt = i / nt, k = i % nt;
+        sv[i] = k < vdim ? to_f(in[(size_t)(start + j0 + tt) * ld + col_v + h * vdim + k]) : 0.0f;
+      }
     }
     __syncthreads();
+    if (ahead && j0 + TB < cnt) fetch(j0 + TB, min(TB, cnt - j0 - TB));
     for (int tt = 0; tt < nb; ++tt) {
       const float* fs = sf + tt * DR;
       const float* qs = sq + tt * DR;
       const float v = sv[tt * nt + tid];
       float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
 #pragma unroll
-      for (int i = 0; i < DR; i += 4) {
+      for (int i = 0; i < DR; i += 4) {                        // S <- f S + (1 - f) v, written as v + f (S - v)
         const float4 f4 = *reinterpret_cast<const float4*>(&fs[i]);
         const float4 q4 = *reinterpret_cast<const float4*>(&qs[i]);
-        S[i] = fmaf(f4.x, S[i], (1.0f - f4.x) * v); S[i + 1] = fmaf(f4.y, S[i + 1], (1.0f - f4.y) * v);
-        S[i + 2] = fmaf(f4.z, S[i + 2], (1.0f - f4.z) * v); S[i + 3] = fmaf(f4.w, S[i + 3], (1.0f - f4.w) * v);
+        S[i] = fmaf(f4.x, S[i] - v, v); S[i + 1] = fmaf(f4.y, S[i + 1] - v, v);
+        S[i + 2] = fmaf(f4.z, S[i + 2] - v, v); S[i + 3] = fmaf(f4.w, S[i + 3] - v, v);
         p0 = fmaf(S[i], q4.x, p0); p1 = fmaf(S[i + 1], q4.y, p1);
         p2 = fmaf(S[i + 2], q4.z, p2); p3 = fmaf(S[i + 3], q4.w, p3);
       }
@@ -407,7 +490,7 @@ glr_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_f, int
       const float v = to_f(in[t * ld + col_v + h * vdim + c]);
       float o = 0.0f;
       for (int i = 0; i < dim; ++i) {
-        const float s = fmaf(fs[i], S[(size_t)i * vdim + c], (1.0f - fs[i]) * v);
+        const float s = fmaf(fs[i], S[(size_t)i * vdim + c] - v, v);
         S[(size_t)i * vdim + c] = s;
         o = fmaf(s, qs[i], o);
       }
