@@ -5,6 +5,7 @@
 #include <math.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -986,7 +987,8 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
   const bool tc_experts = std::is_same<AT, bf16>::value && L.w_gu_t != nullptr;
   // a handful of pairs: one block row per pair; beyond that the sorted order, where pairs that share an expert share its
   // stream (measured at 8 tokens x 4 experts of 32: the tensor-core product over the sorted order is 2.5 - 5 times faster)
-  const bool few = P <= (tc_experts ? 8 : 16);
+  static const int rows_max_env = getenv("HY_EXPERT_ROWS_MAX") ? atoi(getenv("HY_EXPERT_ROWS_MAX")) : -1;   // developer switch
+  const bool few = P <= (rows_max_env >= 0 ? rows_max_env : tc_experts ? 8 : 16);
   {
     ProfScope ps(h, HY_PROF_ROUTE);
     gemm<AT, WT, float>(h, hb, W, (const WT*)L.w_router, W, T, NE, W, to_buf(h->f1, h->ld_f1), L.w_router_t);

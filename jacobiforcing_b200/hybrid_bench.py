@@ -214,12 +214,14 @@ def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], pe
     rt.load_state_dict(w)
     del w
     rng = np.random.default_rng(seed + 1)
-    toks = rng.integers(0, sz["vocab"], prompt + decode_steps + 1).tolist()
+    # every request decodes its own token stream (routed layers would otherwise send all of a batch to the same experts)
+    toks_all = [rng.integers(0, sz["vocab"], prompt + decode_steps + 1).tolist() for _ in range(maxb)]
     costs = _hybrid_costs(desc, hc)
     out = {"size": size, "description": {k: sz[k] for k in sz}, "memory": rt.memory_info()}
 
     def prefill(slot):
         ms, at = 0.0, 0
+        toks = toks_all[slot]
         pages = list(range(slot * pages_per, (slot + 1) * pages_per))
         while at < prompt:
             n = min(2048, prompt - at)
@@ -247,7 +249,7 @@ def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], pe
     for B in batches:
         for s in range(B):
             prefill(s)
-        entries = lambda step: [([toks[prompt + step]], prompt + step, s, list(range(s * pages_per, (s + 1) * pages_per)))
+        entries = lambda step: [([toks_all[s][prompt + step]], prompt + step, s, list(range(s * pages_per, (s + 1) * pages_per)))
                                 for s in range(B)]
         for step in range(3):
             rt.step(entries(step), list(range(B)), want_logits=False, sample=True)
