@@ -825,7 +825,14 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
   const float eps = h->m.norm_eps;
   cudaStream_t s = h->stream;
   AT* hb = (AT*)h->hbuf; AT* pin = (AT*)h->pin; AT* cat = (AT*)h->cat; AT* cv = (AT*)h->cv;
-  {
+  // the input norms are element-wise: every sublayer's epilogue also writes the NEXT sublayer's normed input, so only the
+  // first layer runs a norm kernel of its own
+  const bool routed = c.ff_kind == HY_FF_ROUTED;
+  const bool last = li + 1 == h->lc.size();
+  const TanhNorm none{};
+  const TanhNorm after_mixer = routed ? L.n2 : last ? none : h->lw[li + 1].n1;
+  const TanhNorm after_ff = last ? none : h->lw[li + 1].n1;
+  if (li == 0) {
     ProfScope ps(h, HY_PROF_NORM);
     tanh_norm_kernel<AT><<<T, 256, 0, s>>>(h->x, nullptr, L.n1, W, hb);
     h->launches++;
@@ -974,16 +981,12 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
   }
   {
     ProfScope ps(h, HY_PROF_GEMM_OUT);
-    GemmOut o{nullptr, 0, 0, nullptr, 0, 0, h->x, W, 1.0f, L.n1b.w, L.n1b.b, L.ls1, L.n1b.alpha};
+    GemmOut o{nullptr, 0, 0, nullptr, 0, 0, h->x, W, 1.0f, L.n1b.w, L.n1b.b, L.ls1, L.n1b.alpha,
+              after_mixer.w, after_mixer.b, after_mixer.alpha, hb, std::is_same<AT, float>::value ? 1 : 0};
     gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_out, L.k_out, T, W, L.k_out, o, L.w_out_t);
   }
-  if (c.ff_kind != HY_FF_ROUTED) return HY_OK;
+  if (!routed) return HY_OK;
   const int NE = c.x_experts, top = c.x_top, ff = c.ff, P = T * top, ldh = (ff + 7) & ~7;
-  {
-    ProfScope ps(h, HY_PROF_NORM);
-    tanh_norm_kernel<AT><<<T, 256, 0, s>>>(h->x, nullptr, L.n2, W, hb);
-    h->launches++;
-  }
   const bool tc_experts = std::is_same<AT, bf16>::value && L.w_gu_t != nullptr;
   // a handful of pairs: one block row per pair; beyond that the sorted order, where pairs that share an expert share its
   // stream (measured at 8 tokens x 4 experts of 32: the tensor-core product over the sorted order is 2.5 - 5 times faster)
@@ -1041,7 +1044,7 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
       expert_gemm_simt_kernel<AT, WT, float, false><<<dim3((W + 63) / 64, tiles), 256, 0, s>>>(
           pin, ldh, nullptr, (const WT*)L.w_down, (size_t)W * ff, W, ff, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, ys, W);
     }
-    expert_combine_kernel<<<T, 256, 0, s>>>(ys, W, few ? nullptr : h->x_pair_row, h->x_wts, top, W, L.n2b, L.ls2, h->x);
+    expert_combine_kernel<AT><<<T, 256, 0, s>>>(ys, W, few ? nullptr : h->x_pair_row, h->x_wts, top, W, L.n2b, L.ls2, h->x, after_ff, hb);
     h->launches += 3;
   }
   return HY_OK;

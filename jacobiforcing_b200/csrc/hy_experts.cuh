@@ -209,9 +209,12 @@ __global__ void __launch_bounds__(256) expert_rows_kernel(const TA* __restrict__
 
 // x[t] += ls * (tanh(alpha y) w + b),  y = sum_k wts[t, k] rows[pair_row ? pair_row[t top + k] : t top + k]  (k in order).
 // post.w == NULL: x[t] += y (designs without an output norm on the feed-forward).
+// next.w != NULL: the updated stream also leaves through the next layer's input norm into next_out [T, width].
+template <typename AT>
 __global__ void expert_combine_kernel(const float* __restrict__ rows, int ldr, const int* __restrict__ pair_row,
                                       const float* __restrict__ wts, int top, int width, TanhNorm post,
-                                      const float* __restrict__ ls, float* __restrict__ x) {
+                                      const float* __restrict__ ls, float* __restrict__ x, TanhNorm next,
+                                      AT* __restrict__ next_out) {
   const int t = blockIdx.x;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float y = 0.0f;
@@ -220,7 +223,9 @@ __global__ void expert_combine_kernel(const float* __restrict__ rows, int ldr, c
       y = fmaf(wts[i], rows[(size_t)(pair_row ? pair_row[i] : i) * ldr + c], y);
     }
     if (post.w) y = ls[c] * fmaf(tanhf(post.alpha * y), post.w[c], post.b[c]);
-    x[(size_t)t * width + c] += y;
+    const float v = x[(size_t)t * width + c] + y;
+    x[(size_t)t * width + c] = v;
+    if (next.w) next_out[(size_t)t * width + c] = from_f<AT>(fmaf(tanhf(next.alpha * v), next.w[c], next.b[c]));
   }
 }
 

@@ -118,10 +118,13 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 // hidden activation leaves the merged input projection already activated).  With post_w set, the residual receives
 // post_ls[n] * (tanh(post_alpha c) post_w[n] + post_b[n]): a sublayer's output norm (element-wise, so it needs no second
 // pass) and its layer scale, applied to the fp32 accumulator.
+// With next_w set as well, the element of the updated residual also leaves through the NEXT sublayer's input norm
+// (tanh(next_alpha x) next_w[n] + next_b[n]) into next_out [T, ldr] in the activation type: no separate norm launch.
 struct GemmOut {
   void* out1; int ld1; int split; void* out2; int ld2; int act2;
   float* resid; int ldr; float alpha;
   const float* post_w; const float* post_b; const float* post_ls; float post_alpha;
+  const float* next_w; const float* next_b; float next_alpha; void* next_out; int next_f32;
 };
 
 template <typename TO>
@@ -129,7 +132,13 @@ __device__ __forceinline__ void gemm_store(const GemmOut& o, int t, int n, float
   c *= o.alpha;
   if (o.resid) {
     if (o.post_w) c = o.post_ls[n] * fmaf(tanhf(o.post_alpha * c), o.post_w[n], o.post_b[n]);
-    o.resid[(size_t)t * o.ldr + n] += c;
+    const float v = o.resid[(size_t)t * o.ldr + n] + c;
+    o.resid[(size_t)t * o.ldr + n] = v;
+    if (o.next_w) {
+      const float y = fmaf(tanhf(o.next_alpha * v), o.next_w[n], o.next_b[n]);
+      if (o.next_f32) ((float*)o.next_out)[(size_t)t * o.ldr + n] = y;
+      else ((bf16*)o.next_out)[(size_t)t * o.ldr + n] = __float2bfloat16_rn(y);
+    }
     return;
   }
   if (n < o.split) { ((TO*)o.out1)[(size_t)t * o.ld1 + n] = from_f<TO>(c); return; }
